@@ -1,0 +1,426 @@
+// FP8 (e4m3fn x e4m3fn -> fp32 -> bf16) "NT" GEMMs for sm_100a on the 5th-generation tensor
+// cores: tcgen05.mma kind::f8f6f4 with the accumulator in tensor memory (TMEM), operands
+// staged by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a multi-stage shared-memory
+// ring, warp-specialised roles and a persistent tile loop.
+//
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..   epilogue: TMEM -> registers (tcgen05.ld) -> scale -> bf16 -> global
+//
+// Two scale schemes share the pipeline:
+//   * per-token / per-channel (kBlockScale = false): the whole K extent accumulates in TMEM
+//     (two accumulator buffers, so the epilogue of tile i overlaps the main loop of tile i+1);
+//     the epilogue multiplies by sa[m] * sb[n] and adds the optional bias.
+//   * block scales (kBlockScale = true): scales are arbitrary fp32 per 128-wide K block, which
+//     the tensor core cannot apply, so every K block is a fresh 128 x BN partial product in one
+//     of two TMEM buffers and the epilogue warps promote it: acc += partial * (sa[m,kb] * sb[kb,n])
+//     in registers, while the tensor core already works on the next K block.
+//
+// Every mbarrier wait is bounded (tc_common.cuh): on a timeout the CTA records an error bit in
+// the device status word (read by hkb_check_status), stops issuing work, and still frees TMEM.
+#include "tc_common.cuh"
+
+#include <mutex>
+
+namespace hkb {
+
+// ---- host: tensor-map encoder -----------------------------------------------------------------
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+std::once_flag g_encode_once;
+}  // namespace
+
+int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
+                    uint64_t batch, uint32_t box_rows) {
+    std::call_once(g_encode_once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<EncodeFn>(fn);
+    });
+    HKB_REQUIRE(g_encode != nullptr, HKB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    HKB_REQUIRE(aligned16(base) && row_bytes % 16 == 0, HKB_ERR_BAD_ALIGN,
+                "TMA operands need a 16-byte aligned base and row pitch (pitch %llu bytes)", (unsigned long long)row_bytes);
+    const cuuint64_t dims[3] = {row_bytes, rows, batch};
+    const cuuint64_t strides[2] = {row_bytes, row_bytes * rows};
+    const cuuint32_t box[3] = {128, box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HKB_REQUIRE(r == CUDA_SUCCESS, HKB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return HKB_OK;
+}
+
+namespace {
+
+constexpr int BM = 128;        // tile rows = TMEM lanes
+constexpr int BK = 128;        // bytes (= e4m3 elements) of K per stage = one 128-byte swizzle row
+constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int GROUP_M = 8;
+
+struct GemmParams {
+    int M, N, K, batch;
+    int m_blks, n_blks;
+    int a_box_rows;            // rows of A that TMA actually fetches per tile (<= BM)
+    const float* sa;           // pts: [batch, M]      blockscale: [M, K/128]
+    const float* sb;           // pts: [batch, N]      blockscale: [K/128, N/gn]
+    const __nv_bfloat16* bias; // pts only: [batch, N] or null
+    __nv_bfloat16* C;          // [batch, M, N]
+    int gn;                    // blockscale: 1 or 128
+    uint32_t* status;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int kABytes = BM * BK;
+    static constexpr int kBBytes = BN * BK;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarOffset = STAGES * kStageBytes;
+    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;   // slack for the manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void store_bf16x8(__nv_bfloat16* dst, const float* v) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6], v[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0);
+    o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2);
+    o.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(dst) = o;
+}
+
+// Writes 32 consecutive columns of one output row (N % 8 == 0 keeps 16-byte stores aligned).
+__device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N, const float* v) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8)
+        if (col0 + j < N) store_bf16x8(crow + col0 + j, v + j);
+}
+
+template <int BN, int STAGES, bool kBlockScale, bool kGn128>
+__global__ void __launch_bounds__(64 + 128 * (BN == 256 ? 2 : 1), 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    using L = SmemLayout<BN, STAGES>;
+    constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
+    constexpr int EPI_WARPS = 4 * EPI_GROUPS;
+    constexpr int COLS_PER_GROUP = BN / EPI_GROUPS;
+    constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    constexpr uint32_t IDESC = idesc_f8(BM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + L::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kblocks = p.K / BK;
+    const int tiles_per_batch = p.m_blks * p.n_blks;
+    const int total_tiles = tiles_per_batch * p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), EPI_WARPS);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            prefetch_tmap(&tmA);
+            prefetch_tmap(&tmB);
+            const uint32_t stage_tx = (uint32_t)p.a_box_rows * BK + (uint32_t)L::kBBytes;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int b = t / tiles_per_batch;
+                int mb, nb;
+                tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t sa = smem_base + s * L::kStageBytes;
+                    tma_load_3d(sa, &tmA, full_bar(s), kb * BK, mb * BM, b);
+                    tma_load_3d(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN, b);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                if (!kBlockScale) {
+                    if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                    tc_fence_after();
+                }
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (kBlockScale) {
+                        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                        tc_fence_after();
+                    }
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * L::kStageBytes;
+                    const uint64_t da = smem_desc_sw128(sa);
+                    const uint64_t db = smem_desc_sw128(sa + L::kABytes);
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint32_t accumulate = kBlockScale ? (k != 0) : ((kb | k) != 0);
+                        // advancing K by 32 bytes inside the 128-byte swizzle row = +2 in the address field
+                        mma_f8(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), IDESC, accumulate);
+                    }
+                    tc_commit(empty_bar(s));           // smem stage free once these MMAs retire
+                    if (kBlockScale) {
+                        tc_commit(tfull_bar(acc));      // partial product ready for promotion
+                        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (!kBlockScale && ok) {
+                    tc_commit(tfull_bar(acc));
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ================= epilogue =================
+        const int ew = warp - 2;                 // 0 .. EPI_WARPS-1
+        const int quarter = warp & 3;            // TMEM lane quarter this warp may read
+        const int grp = ew >> 2;                 // column group
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const int b = t / tiles_per_batch;
+            int mb, nb;
+            tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+            const int row = mb * BM + row_in_tile;
+            const bool row_ok = row < p.M;
+            const int col_base = nb * BN + grp * COLS_PER_GROUP;
+            __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
+
+            if constexpr (!kBlockScale) {
+                const float sa = row_ok ? __ldg(p.sa + (int64_t)b * p.M + row) : 0.0f;
+                const float* sbp = p.sb + (int64_t)b * p.N;
+                const __nv_bfloat16* biasp = p.bias ? p.bias + (int64_t)b * p.N : nullptr;
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
+#pragma unroll 1
+                for (int c = 0; c < COLS_PER_GROUP; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(t_addr + c, r);
+                    tmem_ld_wait();
+                    const int col0 = col_base + c;
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        const float sbv = col < p.N ? __ldg(sbp + col) : 0.0f;
+                        float x = __uint_as_float(r[j]) * sa * sbv;
+                        if (biasp && col < p.N) x += __bfloat162float(biasp[col]);
+                        v[j] = x;
+                    }
+                    if (row_ok) store_row32(crow, col0, p.N, v);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            } else {
+                float accv[COLS_PER_GROUP];
+#pragma unroll
+                for (int j = 0; j < COLS_PER_GROUP; ++j) accv[j] = 0.0f;
+                const int kbs = kblocks;
+                const float* sarow = p.sa + (int64_t)(row_ok ? row : p.M - 1) * kbs;
+                const int nsb = p.N / p.gn;                       // columns of sb
+                float sa_next = __ldg(sarow);
+                for (int kb = 0; kb < kbs; ++kb) {
+                    const float sa = sa_next;
+                    if (kb + 1 < kbs) sa_next = __ldg(sarow + kb + 1);
+                    const float* sbrow = p.sb + (int64_t)kb * nsb;
+                    float s_scalar = 0.0f;
+                    if constexpr (kGn128) s_scalar = sa * __ldg(sbrow + min(col_base / 128, nsb - 1));
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
+#pragma unroll
+                    for (int c = 0; c < COLS_PER_GROUP; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(t_addr + c, r);
+                        tmem_ld_wait();
+                        if constexpr (kGn128) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) accv[c + j] = __fmaf_rn(__uint_as_float(r[j]), s_scalar, accv[c + j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const int col = min(col_base + c + j, p.N - 1);
+                                accv[c + j] = __fmaf_rn(__uint_as_float(r[j]), sa * __ldg(sbrow + col), accv[c + j]);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+                if (ok && row_ok) {
+#pragma unroll
+                    for (int c = 0; c < COLS_PER_GROUP; c += 32) store_row32(crow, col_base + c, p.N, accv + c);
+                }
+            }
+        }
+    }
+
+    // ---- teardown: every role is done (or has given up); free TMEM ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
+            // give copies that may still be in flight time to land before the CTA exits
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+    using L = SmemLayout<BN, STAGES>;
+    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128>;
+    // the attribute is per device; set it on every call (cheap) so multi-device processes work
+    const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    HKB_REQUIRE(attr_err == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(attr_err));
+    const int tiles = p.m_blks * p.n_blks * p.batch;
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
+    const int grid = tiles < sms ? tiles : sms;
+    constexpr int threads = 64 + 128 * (BN == 256 ? 2 : 1);
+    kern<<<grid, threads, L::kDynamic, st>>>(tmA, tmB, p);
+    return check_launch("gemm_fp8_kernel");
+}
+
+int common_checks(const char* who, const void* A, const void* B, const void* C, int64_t batch, int64_t M, int64_t N, int64_t K) {
+    HKB_REQUIRE(A && B && C, HKB_ERR_BAD_ARG, "%s: null pointer", who);
+    HKB_REQUIRE(batch >= 1 && M >= 1 && N >= 1 && K >= 1, HKB_ERR_BAD_SHAPE, "%s: empty problem (batch=%lld M=%lld N=%lld K=%lld)", who,
+                (long long)batch, (long long)M, (long long)N, (long long)K);
+    HKB_REQUIRE(K % BK == 0, HKB_ERR_BAD_SHAPE, "%s: K=%lld must be a multiple of %d", who, (long long)K, BK);
+    HKB_REQUIRE(N % 8 == 0, HKB_ERR_BAD_SHAPE, "%s: N=%lld must be a multiple of 8", who, (long long)N);
+    HKB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) && batch < 65536, HKB_ERR_BAD_SHAPE, "%s: dimension too large", who);
+    HKB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C), HKB_ERR_BAD_ALIGN, "%s: A, B and C must be 16-byte aligned", who);
+    return HKB_OK;
+}
+
+}  // namespace
+}  // namespace hkb
+
+extern "C" {
+
+int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, const float* sb, const void* bias,
+                     int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+    using namespace hkb;
+    int rc = common_checks("gemm_fp8_pts", A, B, C, batch, M, N, K);
+    if (rc != HKB_OK) return rc;
+    HKB_REQUIRE(sa && sb, HKB_ERR_BAD_ARG, "gemm_fp8_pts: null scale pointer");
+    GemmParams p{};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.sa = sa; p.sb = sb; p.bias = (const __nv_bfloat16*)bias; p.C = (__nv_bfloat16*)C; p.gn = 0;
+    rc = status_word(&p.status);
+    if (rc != HKB_OK) return rc;
+    p.m_blks = (int)((M + BM - 1) / BM);
+    // Skinny M: fetch only the rows that exist (rounded up to 8); the remaining rows of the
+    // smem tile hold stale bytes that only reach accumulator rows >= M, which are never stored.
+    p.a_box_rows = M >= BM ? BM : (int)((M + 7) / 8 * 8);
+    // Tile width: small problems (few tiles per SM) take narrower tiles so that the SMs stay busy;
+    // skinny-M (decode) shapes are HBM-bound on B and want many independent B streams.
+    const int sms = sm_count();
+    int bn = 256;
+    if (N % 256 != 0 && N < 4096) bn = 128;
+    if ((int64_t)p.m_blks * ((N + 255) / 256) * batch < 2LL * sms) bn = 128;
+    if ((int64_t)p.m_blks * ((N + 127) / 128) * batch < 2LL * sms) bn = 64;
+    p.n_blks = (int)((N + bn - 1) / bn);
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, (uint32_t)p.a_box_rows);
+    if (rc != HKB_OK) return rc;
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint32_t)bn);
+    if (rc != HKB_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, p, st);
+    if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, p, st);
+    return launch_gemm<64, 8, false>(tmA, tmB, p, st);
+}
+
+int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
+                            int64_t M, int64_t N, int64_t K, void* stream) {
+    using namespace hkb;
+    int rc = common_checks("gemm_fp8_blockscale", A, B, C, 1, M, N, K);
+    if (rc != HKB_OK) return rc;
+    HKB_REQUIRE(sa && sb, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale: null scale pointer");
+    HKB_REQUIRE(gn == 1 || gn == 128, HKB_ERR_UNSUPPORTED, "gemm_fp8_blockscale: weight scale group along N must be 1 or 128, got %lld", (long long)gn);
+    HKB_REQUIRE(N % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_fp8_blockscale: N=%lld must be a multiple of 128", (long long)N);
+    GemmParams p{};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
+    p.sa = sa; p.sb = sb; p.bias = nullptr; p.C = (__nv_bfloat16*)C; p.gn = (int)gn;
+    rc = status_word(&p.status);
+    if (rc != HKB_OK) return rc;
+    p.m_blks = (int)((M + BM - 1) / BM);
+    p.a_box_rows = BM;
+    const int sms = sm_count();
+    int bn = 256;
+    if (gn != 128 || N % 256 != 0 || (int64_t)p.m_blks * (N / 256) < 2LL * sms) bn = 128;
+    p.n_blks = (int)(N / bn);
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)M, 1, BM);
+    if (rc != HKB_OK) return rc;
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)bn);
+    if (rc != HKB_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (gn == 128) {
+        if (bn == 256) return launch_gemm<256, 4, true, true>(tmA, tmB, p, st);
+        return launch_gemm<128, 6, true, true>(tmA, tmB, p, st);
+    }
+    return launch_gemm<128, 6, true, false>(tmA, tmB, p, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,296 @@
+// MXFP4 x MXFP4 "NT" GEMM for sm_100a: e2m1 codes (two per byte, K-contiguous) with one e8m0
+// scale per 32 K-elements on both operands, fp32 accumulation in TMEM, bf16 output.
+//
+// The tensor core applies the scales itself: tcgen05.mma kind::mxf4.block_scale.scale_vec::2X
+// (K = 64 per instruction) reads the operand tiles from swizzled shared memory and the scale
+// factors from tensor memory.  The scale factors arrive in the caller's row-major layout
+// [rows, K/32]; a small pre-pass (sf_relayout_kernel) rewrites them into library scratch as
+// 512-byte "atoms" (128 rows x 4 scale bytes = 128 rows x 128 K-elements; byte (r%32)*16 +
+// (r/32)*4 + j for row r, scale j), atoms of one 128-row block consecutive along K.  A pipeline
+// stage (256 K-elements) then needs one contiguous 1 KB bulk copy per 128 rows, and the MMA
+// warp moves each atom smem -> TMEM with tcgen05.cp 32x128b.warpx4 right before the MMAs that
+// use it.
+//
+// Roles, ring, bounded waits and teardown are those of the FP8 kernel (gemm_fp8.cu).
+#include "tc_common.cuh"
+
+namespace hkb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int BKB = 128;          // bytes of K per stage (= 256 e2m1 elements)
+constexpr int STAGES = 6;
+constexpr int GROUP_M = 8;
+constexpr int SF_STAGE = 1024;    // scale bytes per 128 rows per stage (two atoms)
+
+struct Mxfp4Params {
+    int M, N, K, batch;
+    int m_blks, n_blks;
+    int katoms;                   // atoms per 128-row block in the scratch: K / 128 rounded up to even
+    const uint8_t* sfa;           // re-laid-out scales of A: [batch, m_blks, katoms, 512]
+    const uint8_t* sfb;           // re-laid-out scales of B: [batch, n_blks, katoms, 512]
+    __nv_bfloat16* C;
+    uint32_t* status;
+};
+
+// Row-major e8m0 [batch, R, K/32] -> atoms [batch, ceil(R/128), katoms_pad, 512 B]; rows past R
+// and atoms past K/128 are written as zero bytes (they meet zero-filled operand data).  One CTA moves 128 rows x 32 atoms through shared memory so that both
+// the global reads (128 B per row) and writes (512 B per atom) are coalesced.
+__global__ void __launch_bounds__(256)
+sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int R, int katoms, int katoms_pad, int rblks) {
+    __shared__ uint32_t tile[32][129];   // [atom in chunk][word in atom], padded
+    const int b = blockIdx.z;
+    const int rb = blockIdx.y;
+    const int ka0 = blockIdx.x * 32;
+    const int t = threadIdx.x;
+    const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src) + (int64_t)b * R * katoms;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int idx = t + i * 256;
+        const int r = idx >> 5, a = idx & 31;
+        const int row = rb * 128 + r;
+        uint32_t v = 0;
+        if (row < R && ka0 + a < katoms) v = __ldg(s32 + (int64_t)row * katoms + ka0 + a);
+        tile[a][(r & 31) * 4 + (r >> 5)] = v;
+    }
+    __syncthreads();
+    uint32_t* d32 = reinterpret_cast<uint32_t*>(dst) + (((int64_t)b * rblks + rb) * katoms_pad + ka0) * 128;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int idx = t + i * 256;
+        const int a = idx >> 7, w = idx & 127;
+        if (ka0 + a < katoms_pad) d32[(int64_t)a * 128 + w] = tile[a][w];
+    }
+}
+
+struct Smem {
+    static constexpr int kABytes = BM * BKB;
+    static constexpr int kBBytes = BN * BKB;
+    static constexpr int kSfaOff = kABytes + kBBytes;
+    static constexpr int kSfbOff = kSfaOff + SF_STAGE;
+    static constexpr int kStageBytes = kSfbOff + SF_STAGE;        // 34 KB, a multiple of 1024
+    static constexpr int kBarOffset = STAGES * kStageBytes;
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kDynamic = kBarOffset + kNumBars * 8 + 16 + 1024;
+};
+
+constexpr uint32_t TMEM_COLS = 512;               // 2 x 128 accumulator + 8 + 8 scale columns, power of two
+constexpr uint32_t TMEM_SFA = 2 * BN;             // columns [256, 264)
+constexpr uint32_t TMEM_SFB = 2 * BN + 8;         // columns [264, 272)
+
+__global__ void __launch_bounds__(192, 1)
+gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Mxfp4Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + Smem::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::kBarOffset + Smem::kNumBars * 8);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kstages = (p.K + 255) / 256;            // a 128-element tail reads zero-filled data and zero scales
+    const int tiles_per_batch = p.m_blks * p.n_blks;
+    const int total_tiles = tiles_per_batch * p.batch;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            prefetch_tmap(&tmA);
+            prefetch_tmap(&tmB);
+            constexpr uint32_t stage_tx = Smem::kABytes + Smem::kBBytes + 2 * SF_STAGE;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int b = t / tiles_per_batch;
+                int mb, nb;
+                tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+                const uint8_t* sfa_row = p.sfa + ((int64_t)b * p.m_blks + mb) * p.katoms * 512;
+                const uint8_t* sfb_row = p.sfb + ((int64_t)b * p.n_blks + nb) * p.katoms * 512;
+                for (int ks = 0; ks < kstages; ++ks) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t st = smem_base + s * Smem::kStageBytes;
+                    tma_load_3d(st, &tmA, full_bar(s), ks * BKB, mb * BM, b);
+                    tma_load_3d(st + Smem::kABytes, &tmB, full_bar(s), ks * BKB, nb * BN, b);
+                    bulk_load(st + Smem::kSfaOff, sfa_row + (int64_t)ks * SF_STAGE, SF_STAGE, full_bar(s));
+                    bulk_load(st + Smem::kSfbOff, sfb_row + (int64_t)ks * SF_STAGE, SF_STAGE, full_bar(s));
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int ks = 0; ks < kstages; ++ks) {
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * Smem::kStageBytes;
+                    const uint64_t da = smem_desc_sw128(st);
+                    const uint64_t db = smem_desc_sw128(st + Smem::kABytes);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {      // the two 128-K atoms of this stage
+                        tc_cp_sf(tmem_base + TMEM_SFA + h * 4, smem_desc_sf(st + Smem::kSfaOff + h * 512));
+                        tc_cp_sf(tmem_base + TMEM_SFB + h * 4, smem_desc_sf(st + Smem::kSfbOff + h * 512));
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {      // 4 x K=64 (32 bytes of each 128-byte row)
+                        const uint32_t h = k >> 1, sf_id = (k & 1) * 2;
+                        mma_mxf4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_mxf4(BM, BN, sf_id, sf_id),
+                                 tmem_base + TMEM_SFA + h * 4, tmem_base + TMEM_SFB + h * 4, (ks | k) != 0);
+                    }
+                    tc_commit(empty_bar(s));
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (ok) {
+                    tc_commit(tfull_bar(acc));
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            const int b = t / tiles_per_batch;
+            int mb, nb;
+            tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+            const int row = mb * BM + row_in_tile;
+            const bool row_ok = row < p.M;
+            __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) break;
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + lane_addr + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(t_addr + c, r);
+                tmem_ld_wait();
+                if (row_ok) {
+                    const int col0 = nb * BN + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (col0 + j < p.N) {
+                            uint4 o;
+                            __nv_bfloat162 q0 = __floats2bfloat162_rn(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
+                            __nv_bfloat162 q1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            __nv_bfloat162 q2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            __nv_bfloat162 q3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            o.x = *reinterpret_cast<uint32_t*>(&q0);
+                            o.y = *reinterpret_cast<uint32_t*>(&q1);
+                            o.z = *reinterpret_cast<uint32_t*>(&q2);
+                            o.w = *reinterpret_cast<uint32_t*>(&q3);
+                            *reinterpret_cast<uint4*>(crow + col0 + j) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (*abort_flag) {
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace
+}  // namespace hkb
+
+extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                              int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(A && B && C && sfa && sfb, HKB_ERR_BAD_ARG, "gemm_mxfp4: null pointer");
+    HKB_REQUIRE(batch >= 1 && M >= 1 && N >= 1 && K >= 1, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: empty problem");
+    HKB_REQUIRE(K % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: K=%lld must be a multiple of 128", (long long)K);
+    HKB_REQUIRE(N % 8 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: N=%lld must be a multiple of 8", (long long)N);
+    HKB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) && batch < 65536, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: dimension too large");
+    HKB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && ((uintptr_t)sfa & 3) == 0 && ((uintptr_t)sfb & 3) == 0,
+                HKB_ERR_BAD_ALIGN, "gemm_mxfp4: A, B, C must be 16-byte and the scale arrays 4-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    Mxfp4Params p{};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.m_blks = (int)((M + BM - 1) / BM);
+    p.n_blks = (int)((N + BN - 1) / BN);
+    const int katoms_src = (int)(K / 128);
+    p.katoms = (katoms_src + 1) & ~1;
+    p.C = (__nv_bfloat16*)C;
+    int rc = status_word(&p.status);
+    if (rc != HKB_OK) return rc;
+
+    // scale re-layout into library-owned scratch (grown on demand, reused across calls)
+    void *sfa_sw = nullptr, *sfb_sw = nullptr;
+    const size_t sfa_bytes = (size_t)batch * p.m_blks * p.katoms * 512;
+    const size_t sfb_bytes = (size_t)batch * p.n_blks * p.katoms * 512;
+    rc = scratch_get(SCRATCH_SFA, sfa_bytes, &sfa_sw);
+    if (rc != HKB_OK) return rc;
+    rc = scratch_get(SCRATCH_SFB, sfb_bytes, &sfb_sw);
+    if (rc != HKB_OK) return rc;
+    {
+        dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)p.m_blks, (unsigned)batch);
+        sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)sfa, (uint8_t*)sfa_sw, (int)M, katoms_src, p.katoms, p.m_blks);
+        dim3 gb((unsigned)((p.katoms + 31) / 32), (unsigned)p.n_blks, (unsigned)batch);
+        sf_relayout_kernel<<<gb, 256, 0, st>>>((const uint8_t*)sfb, (uint8_t*)sfb_sw, (int)N, katoms_src, p.katoms, p.n_blks);
+        rc = check_launch("sf_relayout_kernel");
+        if (rc != HKB_OK) return rc;
+    }
+    p.sfa = (const uint8_t*)sfa_sw;
+    p.sfb = (const uint8_t*)sfb_sw;
+
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)batch, BM);
+    if (rc != HKB_OK) return rc;
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, BN);
+    if (rc != HKB_OK) return rc;
+    const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
+    HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const int tiles = p.m_blks * p.n_blks * p.batch;
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
+    gemm_mxfp4_kernel<<<tiles < sms ? tiles : sms, 192, Smem::kDynamic, st>>>(tmA, tmB, p);
+    return check_launch("gemm_mxfp4_kernel");
+}

@@ -1,0 +1,215 @@
+// MXFP4 dynamic quantizer for sm_100a: e2m1 codes (two per byte, element 2i in the low
+// nibble) with one e8m0 exponent byte per 32 contiguous elements.
+//
+// HBM-bound streaming kernel.  The [M, D] tensor is a flat sequence of 32-element blocks
+// (D % 32 == 0) and the scale array [M, D/32] is the same sequence, so 4 consecutive lanes
+// (8 bf16 each, one 16-byte load) own one block: two shuffles give the block amax, the
+// exponent is read from amax's bit pattern, each lane emits 4 code bytes and every 16th lane
+// emits four scale bytes as one word.
+//
+// Rounding rule of mode 0: nearest E2M1 magnitude of x / 2^e with ties to the SMALLER
+// magnitude, saturating at 6; sign nibble set iff x < 0.  For bf16 inputs x / 2^e carries at
+// most 8 significant bits, so subtracting 2^-12 from |q| turns every tie into a non-tie
+// without moving any other value across a rounding boundary; the hardware round-to-nearest
+// conversion (cvt.rn.satfinite.e2m1x2.f32) then yields exactly that rule.  fp32 inputs (the
+// RMSNorm prologue) and mode 1 (truncation) use explicit threshold compares.
+#include "common.cuh"
+
+namespace hkb {
+namespace {
+
+// eight floats -> eight e2m1 nibbles in one word, element j in bits 4j..4j+3
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&r)[8]) {
+    uint32_t o;
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "mov.b32 %0, {b0, b1, b2, b3};\n"
+        "}"
+        : "=r"(o)
+        : "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]));
+    return o;
+}
+
+__device__ __forceinline__ uint32_t nibble_compare(float q, int mode) {
+    const float a = fabsf(q);
+    uint32_t m;
+    if (mode == HKB_MXFP4_MODE_KERNEL) {
+        m = (a >= 0.5f) + (a >= 1.0f) + (a >= 1.5f) + (a >= 2.0f) + (a >= 3.0f) + (a >= 4.0f) + (a >= 6.0f);
+        return m | ((__float_as_uint(q) >> 28) & 8u);
+    }
+    m = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+    return m | (q < 0.0f ? 8u : 0u);
+}
+
+// block amax -> (scale byte, 2^-e as float)
+template <int MODE>
+__device__ __forceinline__ void block_exponent(float amax, uint32_t& scale_byte, float& inv) {
+    uint32_t bits = __float_as_uint(amax);
+    if (MODE == HKB_MXFP4_MODE_KERNEL) bits = (bits + 0x200000u) & 0xFF800000u;
+    const int biased = (int)(bits >> 23) & 0xFF;
+    int e = biased - 129;               // floor(log2 amax) - 2
+    e = max(-127, min(127, e));         // subnormal or zero amax lands on -127
+    if (biased == 255) e = 127;         // mode 1 can round amax up to infinity: exponent clamps to 127
+    scale_byte = (uint32_t)(e + 127);
+    // 2^-e: exponent field in [1, 254], or the subnormal 2^-127 for e = 127
+    inv = e == 127 ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(127 - e) << 23);
+}
+
+template <int MODE>
+__device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
+    float f[8];
+    unpack8(v, f);
+    if constexpr (MODE == HKB_MXFP4_MODE_KERNEL) {
+        uint32_t o = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o |= nibble_compare(f[j] * inv, MODE) << (4 * j);
+        return o;
+    } else {
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float q = f[j] * inv;
+            const float m = fmaxf(fabsf(q) - 0x1p-12f, 0.0f);
+            r[j] = q < 0.0f ? -m : m;
+        }
+        return cvt_e2m1x8(r);
+    }
+}
+
+// Writes the scale bytes of the 4 blocks a 16-lane group owns.
+__device__ __forceinline__ void store_scales(uint8_t* scales, int64_t c, int64_t total_chunks, uint32_t sb) {
+    const int lane = threadIdx.x & 31;
+    const int g0 = lane & 16;
+    uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, g0) | (__shfl_sync(0xFFFFFFFFu, sb, g0 + 4) << 8) |
+                    (__shfl_sync(0xFFFFFFFFu, sb, g0 + 8) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, g0 + 12) << 24);
+    const int64_t c16 = c & ~(int64_t)15;
+    if (c16 + 16 <= total_chunks) {
+        if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(scales + (c >> 2)) = word;
+    } else if (c < total_chunks && (lane & 3) == 0) {
+        scales[c >> 2] = (uint8_t)sb;
+    }
+}
+
+template <int MODE, int UNROLL>
+__global__ void __launch_bounds__(256)
+quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ codes,
+                   uint8_t* __restrict__ scales, int64_t total_chunks) {
+    const int64_t base = (int64_t)blockIdx.x * (256 * UNROLL) + threadIdx.x;
+    uint4 v[UNROLL];
+#pragma unroll
+    for (int i = 0; i < UNROLL; ++i) {
+        const int64_t c = base + i * 256;
+        v[i] = (c < total_chunks) ? ld_stream16(x + c * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < UNROLL; ++i) {
+        const int64_t c = base + i * 256;
+        float am = amax8(v[i]);
+        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 2));
+        uint32_t sb;
+        float inv;
+        block_exponent<MODE>(am, sb, inv);
+        const uint32_t out = encode8_bf16<MODE>(v[i], inv);
+        if (c < total_chunks) *reinterpret_cast<uint32_t*>(codes + c * 4) = out;
+        store_scales(scales, c, total_chunks, sb);
+    }
+}
+
+// Fused RMSNorm prologue (fp32 values, explicit compares); one CTA per row.
+template <int NCHUNK>
+__global__ void __launch_bounds__(256)
+rmsnorm_quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                           int nchunks, float eps, int mode) {
+    const int64_t row = blockIdx.x;
+    const int t = threadIdx.x;
+    const __nv_bfloat16* xr = x + row * (int64_t)nchunks * 8;
+    uint4 v[NCHUNK];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * 256;
+        v[i] = (c < nchunks) ? ld_stream16(xr + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
+        float f[8];
+        unpack8(v[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = __fmaf_rn(f[j], f[j], ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    __shared__ float s_ss[8];
+    if ((t & 31) == 0) s_ss[t >> 5] = ss;
+    __syncthreads();
+    ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += s_ss[k];
+    const float rinv = rsqrtf(ss / (float)(nchunks * 8) + eps);
+    const int64_t row_chunks = (int64_t)nchunks;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const int c = t + i * 256;
+        const bool ok = c < nchunks;
+        float f[8], g[8];
+        unpack8(v[i], f);
+        const uint4 wv = ok ? *reinterpret_cast<const uint4*>(w + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
+        unpack8(wv, g);
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            f[j] = f[j] * rinv * g[j];
+            am = fmaxf(am, fabsf(f[j]));
+        }
+        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 2));
+        uint32_t sb;
+        float inv;
+        if (mode == HKB_MXFP4_MODE_KERNEL) block_exponent<HKB_MXFP4_MODE_KERNEL>(am, sb, inv);
+        else block_exponent<HKB_MXFP4_MODE_DOC>(am, sb, inv);
+        uint32_t out = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out |= nibble_compare(f[j] * inv, mode) << (4 * j);
+        const int64_t gc = row * row_chunks + c;
+        if (ok) {
+            *reinterpret_cast<uint32_t*>(codes + gc * 4) = out;
+            if ((t & 3) == 0) scales[gc >> 2] = (uint8_t)sb;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace hkb
+
+extern "C" int hkb_quant_mxfp4(const void* x, const void* w, void* codes, void* scales,
+                               int64_t M, int64_t D, float eps, int mode, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(x && codes && scales, HKB_ERR_BAD_ARG, "quant_mxfp4: null pointer");
+    HKB_REQUIRE(mode == HKB_MXFP4_MODE_DOC || mode == HKB_MXFP4_MODE_KERNEL, HKB_ERR_BAD_ARG, "quant_mxfp4: unknown mode %d", mode);
+    HKB_REQUIRE(M >= 0 && D > 0 && D % 32 == 0, HKB_ERR_BAD_SHAPE, "quant_mxfp4: need D %% 32 == 0, got M=%lld D=%lld", (long long)M, (long long)D);
+    HKB_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3) == 0 && ((uintptr_t)scales & 3) == 0 && (!w || aligned16(w)),
+                HKB_ERR_BAD_ALIGN, "quant_mxfp4: x/w must be 16-byte, codes and scales 4-byte aligned");
+    if (M == 0) return HKB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (w) {
+        const int nchunks = (int)(D / 8);
+        HKB_REQUIRE(D <= 32768 && M <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_mxfp4 with RMSNorm: D must be <= 32768");
+        const int n = (nchunks + 255) / 256;
+#define HKB_RMS(NC) rmsnorm_quant_mxfp4_kernel<NC><<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)codes, (uint8_t*)scales, nchunks, eps, mode)
+        if (n <= 1) HKB_RMS(1); else if (n <= 2) HKB_RMS(2); else if (n <= 4) HKB_RMS(4); else if (n <= 8) HKB_RMS(8); else HKB_RMS(16);
+#undef HKB_RMS
+        return check_launch("rmsnorm_quant_mxfp4_kernel");
+    }
+    constexpr int UNROLL = 4;
+    const int64_t total = M * D / 8;
+    const int64_t grid = (total + 256 * UNROLL - 1) / (256 * UNROLL);
+    HKB_REQUIRE(grid <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_mxfp4: tensor too large");
+    if (mode == HKB_MXFP4_MODE_KERNEL)
+        quant_mxfp4_kernel<HKB_MXFP4_MODE_KERNEL, UNROLL><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, total);
+    else
+        quant_mxfp4_kernel<HKB_MXFP4_MODE_DOC, UNROLL><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, total);
+    return check_launch("quant_mxfp4_kernel");
+}

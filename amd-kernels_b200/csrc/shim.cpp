@@ -1,0 +1,333 @@
+// pybind11 shims: the Python-visible modules of the quantized-GEMM path, with the module and
+// function names and the positional argument order of the reference project's bindings
+// (cited per function).  This one source is compiled once per module with
+//   -DHKB_SHIM_NAME=<module> -DHKB_SHIM_<MODULE>
+// Tensors are duck-typed like in the reference (data_ptr / shape are read from the Python
+// object; no torch C++ dependency); unlike the reference the shim also reads dtype, device,
+// stride and contiguity and validates them.  All work happens behind the C ABI of
+// libhkb200.so; a non-zero status becomes a Python RuntimeError carrying hkb_last_error().
+#include <pybind11/pybind11.h>
+
+#include <cstdint>
+#include <cstdlib>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/hkb200.h"
+
+namespace py = pybind11;
+
+namespace {
+
+struct TView {
+    void* ptr = nullptr;
+    std::vector<int64_t> shape;
+    std::string dtype;   // "bfloat16", "float8_e4m3fn", "uint8", "float32", ...
+    int device = -1;     // CUDA ordinal, -1 = not a CUDA tensor
+    int64_t numel = 1;
+    bool none = true;
+    int64_t dim(int i) const { return shape.at(i < 0 ? shape.size() + i : i); }
+    int rank() const { return (int)shape.size(); }
+};
+
+[[noreturn]] void fail(const std::string& m) { throw std::runtime_error(m); }
+
+TView view(const py::object& t, const char* name, bool allow_none = false) {
+    TView v;
+    if (t.is_none()) {
+        if (!allow_none) fail(std::string(name) + ": tensor is None");
+        return v;
+    }
+    v.none = false;
+    v.ptr = reinterpret_cast<void*>(t.attr("data_ptr")().cast<uint64_t>());
+    for (auto d : t.attr("shape").cast<py::tuple>()) {
+        v.shape.push_back(d.cast<int64_t>());
+        v.numel *= v.shape.back();
+    }
+    if (py::hasattr(t, "dtype")) {
+        v.dtype = py::str(t.attr("dtype")).cast<std::string>();
+        auto dot = v.dtype.rfind('.');
+        if (dot != std::string::npos) v.dtype = v.dtype.substr(dot + 1);
+    }
+    if (py::hasattr(t, "is_contiguous") && !t.attr("is_contiguous")().cast<bool>())
+        fail(std::string(name) + ": tensor must be contiguous (row-major, inner stride 1)");
+    if (py::hasattr(t, "device")) {
+        py::object dev = t.attr("device");
+        if (py::str(dev.attr("type")).cast<std::string>() != "cuda")
+            fail(std::string(name) + ": tensor must live on a CUDA device (there is no CPU path)");
+        py::object idx = dev.attr("index");
+        v.device = idx.is_none() ? 0 : idx.cast<int>();
+    }
+    return v;
+}
+
+void want_dtype(const TView& v, const char* name, std::initializer_list<const char*> ok) {
+    if (v.dtype.empty()) return;  // duck-typed object without dtype: trust the caller, as the reference does
+    std::string list;
+    for (const char* d : ok) {
+        if (v.dtype == d) return;
+        list += std::string(list.empty() ? "" : "/") + d;
+    }
+    fail(std::string(name) + ": dtype " + v.dtype + " not accepted (want " + list + ")");
+}
+
+void same_device(std::initializer_list<const TView*> vs) {
+    int dev = -2;
+    for (const TView* v : vs) {
+        if (v->none) continue;
+        if (dev == -2) dev = v->device;
+        else if (dev != v->device) fail("all tensors must be on the same CUDA device");
+    }
+}
+
+// RAII: make the tensors' device current (through torch, which owns the CUDA context) and
+// fetch torch's current stream on it.
+struct Launch {
+    py::object guard;
+    void* stream = nullptr;
+    explicit Launch(int device) {
+        if (device < 0) return;
+        py::object cuda = py::module_::import("torch").attr("cuda");
+        guard = cuda.attr("device")(device);
+        guard.attr("__enter__")();
+        stream = reinterpret_cast<void*>(cuda.attr("current_stream")(device).attr("cuda_stream").cast<uint64_t>());
+    }
+    ~Launch() {
+        if (guard) guard.attr("__exit__")(py::none(), py::none(), py::none());
+    }
+};
+
+void check(int rc) {
+    if (rc != HKB_OK) fail(std::string(hkb_last_error()) + " [hkb status " + std::to_string(rc) + "]");
+}
+
+int mxfp4_mode(const py::object& mode) {
+    std::string m;
+    if (!mode.is_none()) m = py::str(mode).cast<std::string>();
+    else if (const char* e = std::getenv("HKB_MXFP4_MODE")) m = e;
+    if (m.empty() || m == "doc" || m == "0") return HKB_MXFP4_MODE_DOC;
+    if (m == "kernel" || m == "1") return HKB_MXFP4_MODE_KERNEL;
+    fail("unknown MXFP4 mode '" + m + "' (want 'doc' or 'kernel')");
+}
+
+// ---- quantizers ----------------------------------------------------------------------------
+
+// per_token_quant_fwd(input, output, scales): kernels/quantization/quant/kernel.cpp:159-171.
+// The code type follows output.dtype: float8_e4m3fn / uint8 -> FP8 (amax/448); int8 -> the
+// reference's INT8 mode (amax/127).  Any D % 8 == 0 is accepted (the reference: 4 fixed sizes).
+[[maybe_unused]] void per_token_quant_fwd(py::object input, py::object output, py::object scales) {
+    TView x = view(input, "input"), q = view(output, "output"), s = view(scales, "scales");
+    want_dtype(x, "input", {"bfloat16"});
+    want_dtype(q, "output", {"float8_e4m3fn", "uint8", "int8"});
+    want_dtype(s, "scales", {"float32"});
+    if (x.rank() != 2) fail("input must be [M, D]");
+    const int64_t M = x.dim(0), D = x.dim(1);
+    if (q.numel != M * D) fail("output must have M*D elements");
+    if (s.numel != M) fail("scales must have M elements");
+    same_device({&x, &q, &s});
+    Launch L(x.device);
+    if (q.dtype == "int8") check(hkb_quant_int8_per_token(x.ptr, q.ptr, (float*)s.ptr, M, D, D, L.stream));
+    else check(hkb_quant_fp8_per_token(x.ptr, q.ptr, (float*)s.ptr, M, D, D, L.stream));
+}
+
+// fused_rmsnorm_fp8_quant_fwd(input, weight, output, scales, eps):
+// kernels/quantization/fused_fp8_quant/kernel.cpp:262-275.  weight=None -> pure 1x128 quantizer.
+[[maybe_unused]] void fused_rmsnorm_fp8_quant_fwd(py::object input, py::object weight, py::object output,
+                                                  py::object scales, float eps) {
+    TView x = view(input, "input"), w = view(weight, "weight", true), q = view(output, "output"), s = view(scales, "scales");
+    want_dtype(x, "input", {"bfloat16"});
+    if (!w.none) want_dtype(w, "weight", {"bfloat16"});
+    want_dtype(q, "output", {"float8_e4m3fn", "uint8"});
+    want_dtype(s, "scales", {"float32"});
+    if (x.rank() != 2) fail("input must be [M, D]");
+    const int64_t M = x.dim(0), D = x.dim(1);
+    if (D % 128 != 0) fail("Unsupported D=" + std::to_string(D) + ": D must be a multiple of 128");
+    if (!w.none && w.numel != D) fail("weight must have D elements");
+    if (q.numel != M * D) fail("output must have M*D elements");
+    if (s.numel != M * (D / 128)) fail("scales must have M*(D/128) elements");
+    same_device({&x, &w, &q, &s});
+    Launch L(x.device);
+    check(hkb_quant_fp8_1x128(x.ptr, w.none ? nullptr : w.ptr, q.ptr, (float*)s.ptr, M, D, eps, L.stream));
+}
+
+// Not in the reference: 128x128 block quantizer that produces the weight operand and the
+// transposed b_scale [K/128, N/128] the block-scale GEMM consumes.
+[[maybe_unused]] void weight_quant_128x128(py::object weight, py::object output, py::object scales) {
+    TView w = view(weight, "weight"), q = view(output, "output"), s = view(scales, "scales");
+    want_dtype(w, "weight", {"bfloat16"});
+    want_dtype(q, "output", {"float8_e4m3fn", "uint8"});
+    want_dtype(s, "scales", {"float32"});
+    if (w.rank() != 2) fail("weight must be [N, K]");
+    const int64_t N = w.dim(0), K = w.dim(1);
+    if (q.numel != N * K) fail("output must have N*K elements");
+    if (N % 128 || K % 128) fail("N and K must be multiples of 128");
+    if (s.numel != (N / 128) * (K / 128)) fail("scales must have (K/128)*(N/128) elements");
+    same_device({&w, &q, &s});
+    Launch L(w.device);
+    check(hkb_quant_fp8_128x128(w.ptr, q.ptr, (float*)s.ptr, N, K, L.stream));
+}
+
+// fused_rmsnorm_mxfp4_quant_fwd(input, weight, output, scales, eps):
+// kernels/quantization/fused_mxfp4_quant/kernel.cpp:301-314.  weight=None -> pure quantizer.
+[[maybe_unused]] void fused_rmsnorm_mxfp4_quant_fwd(py::object input, py::object weight, py::object output,
+                                                    py::object scales, float eps, py::object mode) {
+    TView x = view(input, "input"), w = view(weight, "weight", true), q = view(output, "output"), s = view(scales, "scales");
+    want_dtype(x, "input", {"bfloat16"});
+    if (!w.none) want_dtype(w, "weight", {"bfloat16"});
+    want_dtype(q, "output", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(s, "scales", {"uint8", "float8_e8m0fnu"});
+    if (x.rank() != 2) fail("input must be [M, D]");
+    const int64_t M = x.dim(0), D = x.dim(1);
+    if (D % 32 != 0) fail("Unsupported D=" + std::to_string(D) + ": D must be a multiple of 32");
+    if (!w.none && w.numel != D) fail("weight must have D elements");
+    if (q.numel != M * D / 2) fail("output must have M*D/2 bytes");
+    if (s.numel != M * (D / 32)) fail("scales must have M*(D/32) bytes");
+    same_device({&x, &w, &q, &s});
+    const int m = mxfp4_mode(mode);
+    Launch L(x.device);
+    check(hkb_quant_mxfp4(x.ptr, w.none ? nullptr : w.ptr, q.ptr, s.ptr, M, D, eps, m, L.stream));
+}
+
+// ---- GEMMs ---------------------------------------------------------------------------------
+
+struct GemmDims { int64_t batch, M, N, K; };
+
+// A [.., M, Ka], B [.., N, Ka], C [.., M, N]; leading dimensions multiply into the batch
+// (the reference pads every tensor to 4-D with leading ones).
+GemmDims gemm_dims(const TView& A, const TView& B, const TView& C, int k_per_byte_num, int k_per_byte_den) {
+    if (A.rank() < 2 || B.rank() < 2 || C.rank() < 2) fail("A, B, C must have at least 2 dimensions");
+    GemmDims d;
+    d.M = A.dim(-2);
+    d.K = A.dim(-1) * k_per_byte_num / k_per_byte_den;
+    d.N = B.dim(-2);
+    if (B.dim(-1) != A.dim(-1)) fail("A and B must have the same K extent (both are K-contiguous: A[M,K], B[N,K])");
+    d.batch = A.numel / (A.dim(-2) * A.dim(-1));
+    if (B.numel / (B.dim(-2) * B.dim(-1)) != d.batch) fail("A and B batch counts differ");
+    if (C.dim(-2) != d.M || C.dim(-1) != d.N || C.numel != d.batch * d.M * d.N) fail("C must be [batch, M, N]");
+    return d;
+}
+
+void fp8_pts(py::object A_, py::object B_, py::object C_, py::object sa_, py::object sb_, py::object bias_) {
+    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale"),
+          bias = view(bias_, "bias", true);
+    want_dtype(A, "A", {"float8_e4m3fn", "uint8"});
+    want_dtype(B, "B", {"float8_e4m3fn", "uint8"});
+    want_dtype(C, "C", {"bfloat16"});
+    want_dtype(sa, "a_scale", {"float32"});
+    want_dtype(sb, "b_scale", {"float32"});
+    if (!bias.none) want_dtype(bias, "bias", {"bfloat16"});
+    GemmDims d = gemm_dims(A, B, C, 1, 1);
+    if (sa.numel != d.batch * d.M) fail("a_scale must have batch*M elements");
+    if (sb.numel != d.batch * d.N) fail("b_scale must have batch*N elements");
+    if (!bias.none && bias.numel != d.batch * d.N) fail("bias must have batch*N elements");
+    same_device({&A, &B, &C, &sa, &sb, &bias});
+    Launch L(A.device);
+    check(hkb_gemm_fp8_pts(A.ptr, B.ptr, C.ptr, (const float*)sa.ptr, (const float*)sb.ptr,
+                           bias.none ? nullptr : bias.ptr, d.batch, d.M, d.N, d.K, L.stream));
+}
+
+// gemm_a8w8_per_token_scale_tk.dispatch(A, B, C, a_scale, b_scale):
+// kernels/gemm-basic/gemm_a8w8_per_token_scale/kernel.cpp:165-171
+[[maybe_unused]] void dispatch_per_token(py::object A, py::object B, py::object C, py::object sa, py::object sb) {
+    fp8_pts(A, B, C, sa, sb, py::none());
+}
+// gemm_a8w8_tk.dispatch(A, B, a_scale, b_scale, C): kernels/gemm-basic/gemm_a8w8/kernel.cpp:171-174
+[[maybe_unused]] void dispatch_a8w8(py::object A, py::object B, py::object sa, py::object sb, py::object C) {
+    fp8_pts(A, B, C, sa, sb, py::none());
+}
+// batched_gemm_a8w8_tk.dispatch(A, B, a_scale, b_scale, C, bias):
+// kernels/gemm-batched/batched_gemm_a8w8/kernel.cpp:196-202.  bias present -> added.
+[[maybe_unused]] void dispatch_batched_a8w8(py::object A, py::object B, py::object sa, py::object sb, py::object C, py::object bias) {
+    fp8_pts(A, B, C, sa, sb, bias);
+}
+
+// gemm_a8w8_blockscale_tk.dispatch(A, B, C, a_scale, b_scale):
+// kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:174-180.
+// a_scale [M, K/128]; b_scale [K/128, N/gn], gn = N / b_scale.shape[1] in {1, 128}.
+[[maybe_unused]] void dispatch_blockscale(py::object A_, py::object B_, py::object C_, py::object sa_, py::object sb_) {
+    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale");
+    want_dtype(A, "A", {"float8_e4m3fn", "uint8"});
+    want_dtype(B, "B", {"float8_e4m3fn", "uint8"});
+    want_dtype(C, "C", {"bfloat16"});
+    want_dtype(sa, "a_scale", {"float32"});
+    want_dtype(sb, "b_scale", {"float32"});
+    GemmDims d = gemm_dims(A, B, C, 1, 1);
+    if (d.batch != 1) fail("block-scale GEMM takes 2-D operands");
+    if (d.K % 128) fail("K must be a multiple of 128");
+    const int64_t kb = d.K / 128;
+    if (sa.numel != d.M * kb) fail("a_scale must be [M, K/128]");
+    if (sb.numel % kb) fail("b_scale must be [K/128, N/gn]");
+    const int64_t ncols = sb.numel / kb;
+    if (ncols == 0 || d.N % ncols) fail("b_scale must be [K/128, N/gn]");
+    const int64_t gn = d.N / ncols;
+    if (gn != 1 && gn != 128) fail("b_scale group size along N must be 1 or 128, got " + std::to_string(gn));
+    same_device({&A, &B, &C, &sa, &sb});
+    Launch L(A.device);
+    check(hkb_gemm_fp8_blockscale(A.ptr, B.ptr, C.ptr, (const float*)sa.ptr, (const float*)sb.ptr, gn, d.M, d.N, d.K, L.stream));
+}
+
+// gemm_afp4wfp4_tk.dispatch(A, B, C[, a_scales, b_scales]) and the batched twin:
+// kernels/gemm-basic/gemm_afp4wfp4/kernel.cpp:154-158, kernels/gemm-batched/batched_gemm_afp4wfp4/kernel.cpp:164-167.
+// Operands are the packed form the reference's header comments specify (u8 [.., K/2] codes +
+// e8m0 [.., K/32] scales); the 3-argument bf16 "host-dequantized" form is a bf16 GEMM and is rejected.
+[[maybe_unused]] void dispatch_mxfp4(py::object A_, py::object B_, py::object C_, py::object sfa_, py::object sfb_) {
+    if (sfa_.is_none() || sfb_.is_none())
+        fail("gemm_afp4wfp4: pass packed e2m1 codes plus a_scales and b_scales (e8m0); "
+             "the host-dequantized bf16 form is not supported");
+    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sfa = view(sfa_, "a_scales"), sfb = view(sfb_, "b_scales");
+    want_dtype(A, "A", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(B, "B", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(C, "C", {"bfloat16"});
+    want_dtype(sfa, "a_scales", {"uint8", "float8_e8m0fnu"});
+    want_dtype(sfb, "b_scales", {"uint8", "float8_e8m0fnu"});
+    GemmDims d = gemm_dims(A, B, C, 2, 1);
+    if (sfa.numel != d.batch * d.M * (d.K / 32)) fail("a_scales must be [batch, M, K/32]");
+    if (sfb.numel != d.batch * d.N * (d.K / 32)) fail("b_scales must be [batch, N, K/32]");
+    same_device({&A, &B, &C, &sfa, &sfb});
+    Launch L(A.device);
+    check(hkb_gemm_mxfp4(A.ptr, B.ptr, C.ptr, sfa.ptr, sfb.ptr, d.batch, d.M, d.N, d.K, L.stream));
+}
+
+}  // namespace
+
+#ifndef HKB_SHIM_NAME
+#error "compile with -DHKB_SHIM_NAME=<module name>"
+#endif
+
+PYBIND11_MODULE(HKB_SHIM_NAME, m) {
+    using namespace pybind11::literals;
+#if defined(HKB_SHIM_QUANT)
+    m.doc() = "per-token dynamic quantization (FP8 e4m3fn, or INT8 when output is int8), sm_100a";
+    m.def("per_token_quant_fwd", &per_token_quant_fwd, "input"_a, "output"_a, "scales"_a);
+#elif defined(HKB_SHIM_FUSED_FP8_QUANT)
+    m.doc() = "1x128 block FP8 quantizer with optional fused RMSNorm; 128x128 weight quantizer, sm_100a";
+    m.def("fused_rmsnorm_fp8_quant_fwd", &fused_rmsnorm_fp8_quant_fwd, "input"_a, "weight"_a, "output"_a, "scales"_a, "eps"_a = 1e-6f);
+    m.def("weight_quant_128x128", &weight_quant_128x128, "weight"_a, "output"_a, "scales"_a);
+#elif defined(HKB_SHIM_FUSED_MXFP4_QUANT)
+    m.doc() = "MXFP4 (e2m1 + e8m0 per 32) quantizer with optional fused RMSNorm, sm_100a";
+    m.def("fused_rmsnorm_mxfp4_quant_fwd", &fused_rmsnorm_mxfp4_quant_fwd, "input"_a, "weight"_a, "output"_a, "scales"_a,
+          "eps"_a = 1e-6f, "mode"_a = py::none());
+#elif defined(HKB_SHIM_GEMM_A8W8)
+    m.doc() = "FP8 GEMM with per-row / per-channel scales (argument order A, B, a_scale, b_scale, C), sm_100a tcgen05";
+    m.def("dispatch", &dispatch_a8w8, "A"_a, "B"_a, "a_scale"_a, "b_scale"_a, "C"_a);
+#elif defined(HKB_SHIM_GEMM_A8W8_PER_TOKEN_SCALE)
+    m.doc() = "FP8 GEMM with per-token / per-channel scales, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_per_token, "A"_a, "B"_a, "C"_a, "a_scale"_a, "b_scale"_a);
+#elif defined(HKB_SHIM_GEMM_A8W8_BLOCKSCALE)
+    m.doc() = "FP8 GEMM with 1x128 activation and 128x128 (or 128x1) weight block scales, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_blockscale, "A"_a, "B"_a, "C"_a, "a_scale"_a, "b_scale"_a);
+#elif defined(HKB_SHIM_GEMM_AFP4WFP4)
+    m.doc() = "MXFP4 x MXFP4 GEMM (e2m1 codes, e8m0 scales per 32), sm_100a tcgen05 block-scaled MMA";
+    m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());
+#elif defined(HKB_SHIM_BATCHED_GEMM_A8W8)
+    m.doc() = "batched FP8 GEMM with per-token / per-channel scales and optional bias, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_batched_a8w8, "A"_a, "B"_a, "a_scale"_a, "b_scale"_a, "C"_a, "bias"_a = py::none());
+#elif defined(HKB_SHIM_BATCHED_GEMM_AFP4WFP4)
+    m.doc() = "batched MXFP4 x MXFP4 GEMM, sm_100a tcgen05 block-scaled MMA";
+    m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());
+#else
+#error "unknown shim selector"
+#endif
+    m.def("hkb_version", []() { return hkb_version(); });
+}

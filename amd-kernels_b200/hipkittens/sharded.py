@@ -1,0 +1,66 @@
+"""N-sharded (column-parallel) block-scale FP8 GEMM across the GPUs of one node.
+
+One process per GPU (torch.distributed, NCCL over NVLink).  The weight ``W[N, K]`` and its
+``b_scale[K/128, N/gn]`` are split along N: rank r owns output columns
+``[r*N/g, (r+1)*N/g)``; activations and ``a_scale`` are replicated.  The GEMM itself needs no
+communication -- each rank writes its own ``C_r[M, N/g]``.  Only when the caller asks for the
+assembled ``C[M, N]`` is there a collective: one all-gather of the bf16 shards.
+
+The reference project has no multi-GPU code; this module is the multi-GPU form of
+``hk.gemm.a8w8_blockscale.dispatch`` (kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:51-180).
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(N, world_size, rank, align=128):
+    """Column range [n0, n1) of ``rank``: N is cut into ``align``-wide blocks which are dealt out
+    as evenly as possible (the first ``blocks % world_size`` ranks get one more)."""
+    if N % align:
+        raise ValueError(f"N={N} must be a multiple of {align}")
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    blocks = N // align
+    base, extra = divmod(blocks, world_size)
+    b0 = rank * base + min(rank, extra)
+    b1 = b0 + base + (1 if rank < extra else 0)
+    return b0 * align, b1 * align
+
+
+def shard_weight(Wq, b_scale, world_size, rank):
+    """Slice a quantized weight [N, K] and its b_scale [K/128, N/gn] for ``rank``.
+    Returns contiguous (Wq_r, b_scale_r)."""
+    N = Wq.shape[0]
+    gn = N // b_scale.shape[1]
+    if gn not in (1, 128):
+        raise ValueError(f"b_scale group size along N must be 1 or 128, got {gn}")
+    n0, n1 = shard_bounds(N, world_size, rank)
+    return Wq[n0:n1].contiguous(), b_scale[:, n0 // gn:n1 // gn].contiguous()
+
+
+def _default_gemm(A, B, C, a_scale, b_scale):
+    from . import gemm
+    gemm.a8w8_blockscale.dispatch(A, B, C, a_scale, b_scale)
+
+
+def gemm_a8w8_blockscale(A, Wq_r, C_r, a_scale, b_scale_r, gather=False, group=None, out=None,
+                         gemm_fn=None):
+    """Local shard GEMM ``C_r = blockscale(A, Wq_r)``; with ``gather=True`` also all-gathers the
+    shards and returns the assembled ``[M, N]`` tensor (``out`` if given), else returns ``C_r``.
+
+    All ranks must hold equally sized shards when gathering (N/128 divisible by the world size).
+    ``gemm_fn`` replaces the CUDA GEMM in host-logic tests.
+    """
+    (gemm_fn or _default_gemm)(A, Wq_r, C_r, a_scale, b_scale_r)
+    if not gather:
+        return C_r
+    world = dist.get_world_size(group)
+    M, n_local = C_r.shape
+    blocked = torch.empty((world, M, n_local), dtype=C_r.dtype, device=C_r.device)
+    dist.all_gather_into_tensor(blocked, C_r.contiguous(), group=group)
+    # [g, M, N/g] (what the collective produces) -> [M, N]
+    full = blocked.permute(1, 0, 2).reshape(M, world * n_local)
+    if out is not None:
+        out.copy_(full)
+        return out
+    return full.contiguous()

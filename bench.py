@@ -1,0 +1,514 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" = one pass of the path over one batch of synthetic activations: quantize the bf16
+activations (dynamic, on the GPU) and run the quantized GEMM against resident pre-quantized
+weights.  Prints ONE JSON line (rank 0).
+
+Workloads (shapes and value distributions of the benchmark configurations; inputs are seeded
+synthetic tensors, there is no dataset behind this metric):
+  c2   block-scale FP8, M=4096 N=14336 K=4096 (1x128 / 128x128 scales)        default at --gpus 1
+  c5   block-scale FP8, M=16384 N=57344 K=8192, N-sharded over the ranks       default at --gpus >1
+  c3   MXFP4, M=N=K=8192
+  c4a  per-token FP8, M=16 N=28672 K=8192 (decode shape, HBM-bound)
+  c4b  batched per-token FP8, B=8 M=512 N=4096 K=4096
+  c1   per-token FP8, M=128 N=1024 K=1024 (latency-bound parity configuration)
+  qbw-fp8 / qbw-1x128 / qbw-mxfp4   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192)
+
+`value` is device time with inputs resident in HBM (CUDA events per step on the launching
+stream, L2 flushed between steps, max over ranks); `e2e` is the same metric through the public
+`hipkittens` calls with HOST (pinned) activations and a host copy of the result inside the timed
+region.  `--impl reference` times the CPU oracle (the reference project's PyTorch path restated
+in oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "amd-kernels_b200"))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (kind, batch, M, N, K)
+    "c1": ("pts", 1, 128, 1024, 1024),
+    "c2": ("blockscale", 1, 4096, 14336, 4096),
+    "c3": ("mxfp4", 1, 8192, 8192, 8192),
+    "c4a": ("pts", 1, 16, 28672, 8192),
+    "c4b": ("pts", 8, 512, 4096, 4096),
+    "c5": ("blockscale", 1, 16384, 57344, 8192),
+    "qbw-fp8": ("quant-fp8", 1, 16384, 0, 8192),
+    "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
+    "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),
+}
+METRIC = "quant GEMM TFLOPS & % of FP8/FP4 tensor peak; quantizer GB/s vs HBM peak"
+L2_FLUSH_BYTES = 256 << 20
+
+# DRAM bytes (read + write) of ONE launch of the dominant kernel from an ncu capture, per workload
+# (profiles/ has the captures); None = not captured.
+NCU_TRAFFIC = {}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def flops_of(kind, batch, M, N, K):
+    return 2.0 * batch * M * N * K
+
+
+def quant_bytes(kind, M, D):
+    if kind == "quant-fp8":
+        return M * D * 3 + M * 4
+    if kind == "quant-1x128":
+        return M * D * 3 + M * (D // 128) * 4
+    return M * D * 2 + M * D // 2 + M * D // 32
+
+
+def gemm_bytes(kind, batch, M, N, K):
+    """Unique bytes that must cross HBM once: operand codes + scales + bf16 output."""
+    if kind == "mxfp4":
+        return batch * ((M + N) * K // 2 + (M + N) * K // 32 + M * N * 2)
+    if kind == "blockscale":
+        return M * K + N * K + M * (K // 128) * 4 + (K // 128) * (N // 128) * 4 + M * N * 2
+    return batch * (M * K + N * K + (M + N) * 4 + M * N * 2)
+
+
+class Workload:
+    """Device state of one workload on one rank, plus the step functions."""
+
+    def __init__(self, name, rank, world, dev):
+        import hipkittens as hk
+        from hipkittens import sharded
+        self.hk = hk
+        self.name = name
+        self.kind, self.batch, self.M, N, self.K = WORKLOADS[name]
+        self.dev = dev
+        g = torch.Generator(device=dev).manual_seed(42)
+        M, K, B = self.M, self.K, self.batch
+        if self.kind.startswith("quant"):
+            self.N = 0
+            self.x = torch.randn(M, K, generator=g, device=dev, dtype=torch.float32).bfloat16()
+            if self.kind == "quant-mxfp4":
+                self.q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+                self.s = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+            else:
+                self.q = torch.empty(M, K, dtype=torch.uint8, device=dev)
+                self.s = torch.empty(M, 1 if self.kind == "quant-fp8" else K // 128, dtype=torch.float32, device=dev)
+            self.launches_per_step = 1
+            return
+        # N-sharding: this rank owns columns [n0, n1)
+        n0, n1 = sharded.shard_bounds(N, world, rank) if world > 1 else (0, N)
+        self.N_total, self.N = N, n1 - n0
+        ashape = (M, K) if B == 1 else (B, M, K)
+        wshape = (self.N, K) if B == 1 else (B, self.N, K)
+        A = torch.randn(ashape, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        if self.kind == "blockscale":                      # 1 % outlier channels x20
+            idx = torch.randperm(K, generator=torch.Generator().manual_seed(42))[: K // 100].to(dev)
+            A[..., idx] = (A[..., idx].float() * 20).bfloat16()
+        self.A = A
+        # weights: generated and quantized once, in slabs to bound the bf16 staging memory
+        gw = torch.Generator(device=dev).manual_seed(1000 + rank)
+        if self.kind == "blockscale":
+            self.Wq = torch.empty(self.N, K, dtype=torch.uint8, device=dev)
+            self.sw = torch.empty(K // 128, self.N // 128, dtype=torch.float32, device=dev)
+            slab = 4096
+            for r0 in range(0, self.N, slab):
+                r1 = min(self.N, r0 + slab)
+                w = (torch.randn(r1 - r0, K, generator=gw, device=dev) * 0.02).bfloat16()
+                s = torch.empty(K // 128, (r1 - r0) // 128, dtype=torch.float32, device=dev)
+                hk.weight_quant_128x128(w, self.Wq[r0:r1], s)
+                self.sw[:, r0 // 128:r1 // 128] = s
+            self.Aq = torch.empty(M, K, dtype=torch.uint8, device=dev)
+            self.sa = torch.empty(M, K // 128, dtype=torch.float32, device=dev)
+        elif self.kind == "pts":
+            W = (torch.randn(wshape, generator=gw, device=dev) * 0.02).bfloat16()
+            self.Wq = torch.empty(wshape, dtype=torch.uint8, device=dev)
+            self.sw = torch.empty(B * self.N, 1, dtype=torch.float32, device=dev)
+            hk.per_token_quant_fwd(W.view(-1, K), self.Wq.view(-1, K), self.sw)
+            self.Aq = torch.empty(ashape, dtype=torch.uint8, device=dev)
+            self.sa = torch.empty(B * M, 1, dtype=torch.float32, device=dev)
+        else:  # mxfp4
+            W = (torch.randn(wshape, generator=gw, device=dev) * 0.02).bfloat16()
+            self.Wq = torch.empty(self.N, K // 2, dtype=torch.uint8, device=dev)
+            self.sw = torch.empty(self.N, K // 32, dtype=torch.uint8, device=dev)
+            hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, self.Wq, self.sw, 1e-6)
+            self.Aq = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+            self.sa = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+        cshape = (M, self.N) if B == 1 else (B, M, self.N)
+        self.C = torch.empty(cshape, dtype=torch.bfloat16, device=dev)
+        self.launches_per_step = 2 if self.kind != "mxfp4" else 4     # quant + gemm (+ 2 scale re-layouts)
+        torch.cuda.synchronize()
+
+    # -- device-resident step ------------------------------------------------------------
+    def quantize(self, A):
+        hk, K = self.hk, self.K
+        if self.kind == "blockscale":
+            hk.fused_rmsnorm_fp8_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
+        elif self.kind == "pts":
+            hk.per_token_quant_fwd(A.view(-1, K), self.Aq.view(-1, K), self.sa)
+        elif self.kind == "mxfp4":
+            hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
+        elif self.kind == "quant-fp8":
+            hk.per_token_quant_fwd(self.x, self.q, self.s)
+        elif self.kind == "quant-1x128":
+            hk.fused_rmsnorm_fp8_quant_fwd(self.x, None, self.q, self.s, 1e-6)
+        else:
+            hk.fused_rmsnorm_mxfp4_quant_fwd(self.x, None, self.q, self.s, 1e-6)
+
+    def gemm(self):
+        hk = self.hk
+        if self.kind == "blockscale":
+            hk.gemm.a8w8_blockscale.dispatch(self.Aq, self.Wq, self.C, self.sa, self.sw)
+        elif self.kind == "pts":
+            if self.batch == 1:
+                hk.gemm.a8w8_per_token.dispatch(self.Aq, self.Wq, self.C, self.sa, self.sw)
+            else:
+                hk.batched_gemm.a8w8.dispatch(self.Aq, self.Wq, self.sa, self.sw, self.C, None)
+        elif self.kind == "mxfp4":
+            hk.gemm.afp4wfp4.dispatch(self.Aq, self.Wq, self.C, self.sa, self.sw)
+
+    def step(self):
+        if self.kind.startswith("quant"):
+            self.quantize(None)
+        else:
+            self.quantize(self.A)
+            self.gemm()
+
+    # -- host-to-host step ---------------------------------------------------------------
+    def setup_e2e(self):
+        src = self.x if self.kind.startswith("quant") else self.A
+        self.h_in = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
+        self.h_in.copy_(src)
+        self.d_in = torch.empty_like(src)
+        if self.kind.startswith("quant"):
+            self.h_out = torch.empty(self.q.shape, dtype=self.q.dtype, pin_memory=True)
+            self.h_out2 = torch.empty(self.s.shape, dtype=self.s.dtype, pin_memory=True)
+            self.d2h = self.q.numel() * self.q.element_size() + self.s.numel() * self.s.element_size()
+        else:
+            self.h_out = torch.empty(self.C.shape, dtype=self.C.dtype, pin_memory=True)
+            self.d2h = self.C.numel() * 2
+        self.h2d = src.numel() * src.element_size()
+
+    def step_e2e(self):
+        self.d_in.copy_(self.h_in, non_blocking=True)
+        if self.kind.startswith("quant"):
+            saved = self.x
+            self.x = self.d_in
+            self.quantize(None)
+            self.x = saved
+            self.h_out.copy_(self.q, non_blocking=True)
+            self.h_out2.copy_(self.s, non_blocking=True)
+        else:
+            self.quantize(self.d_in)
+            self.gemm()
+            self.h_out.copy_(self.C, non_blocking=True)
+
+    def work(self, world):
+        """(units of work per step over ALL ranks, unit name)"""
+        if self.kind.startswith("quant"):
+            return quant_bytes(self.kind, self.M, self.K) * world / 1e9, "GB/s"
+        n = self.N_total if world > 1 else self.N
+        return flops_of(self.kind, self.batch, self.M, n, self.K) / 1e12, "TFLOP/s"
+
+
+def timed_loop(fn, steps, warmup, flush):
+    """Per-step CUDA-event timing on the current stream; the L2 flush sits between steps, outside
+    the event pairs.  Returns the summed milliseconds of `steps` steps."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        flush.zero_()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs)
+
+
+def dist_max(x, world, dev):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+CPU_SAMPLE_MAX_N = 16384
+
+
+def cpu_reference_step(name, sample_rows):
+    """One pass of the path on the CPU with the oracle (torch CPU + NumPy), on `sample_rows` rows
+    of the activations and at most CPU_SAMPLE_MAX_N weight rows (all of K).
+    Returns (seconds, units of work done, unit)."""
+    from oracle import gemm as ogemm, quant as oquant
+    kind, B, M, N, K = WORKLOADS[name]
+    if N > CPU_SAMPLE_MAX_N:
+        N = CPU_SAMPLE_MAX_N // 128 * 128
+    g = torch.Generator().manual_seed(42)
+    Ms = min(M, sample_rows)
+    key = (name, Ms)
+    st = cpu_reference_step.cache.get(key)
+    if st is None:
+        A = torch.randn(B * Ms, K, generator=g).bfloat16()
+        st = {"A": A}
+        if not kind.startswith("quant"):
+            Nn = N
+            W = (torch.randn(B * Nn, K, generator=g) * 0.02).bfloat16()
+            if kind == "blockscale":
+                st["Wq"], st["sw"] = oquant.quant_fp8_128x128(W)
+            elif kind == "pts":
+                st["Wq"], st["sw"] = oquant.quant_fp8_per_token(W)
+            else:
+                st["Wq"], st["sw"] = oquant.quant_mxfp4(W)
+        cpu_reference_step.cache[key] = st
+    A = st["A"]
+    t0 = time.perf_counter()
+    if kind == "blockscale":
+        aq, sa = oquant.quant_fp8_1x128(A)
+        C = ogemm.gemm_fp8_blockscale(aq, st["Wq"], sa, st["sw"])
+    elif kind == "pts":
+        aq, sa = oquant.quant_fp8_per_token(A)
+        C = ogemm.gemm_fp8_per_token(aq.reshape(B, Ms, K), st["Wq"].reshape(B, N, K), sa.reshape(B, Ms), st["sw"].reshape(B, N))
+    elif kind == "mxfp4":
+        aq, sa = oquant.quant_mxfp4(A)
+        C = ogemm.gemm_mxfp4(aq, st["Wq"], sa, st["sw"])
+    elif kind == "quant-fp8":
+        C = oquant.quant_fp8_per_token(A)
+    elif kind == "quant-1x128":
+        C = oquant.quant_fp8_1x128(A)
+    else:
+        C = oquant.quant_mxfp4(A)
+    if not kind.startswith("quant"):
+        C = torch.from_numpy(C).bfloat16()
+    dt = time.perf_counter() - t0
+    if kind.startswith("quant"):
+        return dt, quant_bytes(kind, Ms, K) / 1e9, "GB/s"
+    return dt, flops_of(kind, B, Ms, N, K) / 1e12, "TFLOP/s"
+
+
+cpu_reference_step.cache = {}
+
+
+def default_sample_rows(name):
+    kind, B, M, N, K = WORKLOADS[name]
+    if kind.startswith("quant"):
+        return 1024
+    # about 0.3 TFLOP of matmul per step: a second or so on a many-core host
+    rows = int(0.3e12 / (2.0 * B * min(N, CPU_SAMPLE_MAX_N) * K))
+    return max(16, min(M, (rows // 16) * 16 or 16))
+
+
+def run_reference(args, name, world):
+    kind, B, M, N, K = WORKLOADS[name]
+    rows = default_sample_rows(name)
+    for _ in range(args.warmup):
+        cpu_reference_step(name, rows)
+    tot, units, unit = 0.0, 0.0, ""
+    for _ in range(args.steps):
+        dt, u, unit = cpu_reference_step(name, rows)
+        tot += dt
+        units += u
+    value = units / tot
+    sample = (f"{min(M, rows)} of {M} activation rows, {min(N, CPU_SAMPLE_MAX_N)} of {N} weight rows, all of K={K}"
+              + (f", batch {B}" if B > 1 else ""))
+    out = {"impl": "reference", "metric": METRIC, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": tot / args.steps * 1e3, "higher_is_better": True,
+           "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+           "dtype": "f32", "data": "synthetic",
+           "config": {"workload": name, "kind": kind, "batch": B, "M": M, "N": N, "K": K,
+                      "note": "CPU oracle (torch CPU fp32 dequantize-then-matmul + NumPy quantizers), bounded sample"},
+           "cpu_baseline": {"value": value, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+           "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    name = args.workload or ("c2" if world == 1 else "c5")
+
+    if args.impl == "reference":
+        if rank == 0:
+            run_reference(args, name, world)
+        return 0
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device; this path has no CPU fallback"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    peaks = load_peaks()
+    wl = Workload(name, rank, world, dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    units, unit = wl.work(world)
+
+    sampler = ClockSampler(local_rank)
+    barrier(world)
+    if rank == 0:
+        sampler.start()
+    ms = timed_loop(wl.step, args.steps, args.warmup, flush)
+    barrier(world)
+    ms = dist_max(ms, world, dev)
+    clocks = sampler.stop() if rank == 0 else None
+    value = units * args.steps / (ms / 1e3)
+
+    # dominant kernel alone (GEMM; the quantizer for the quantizer workloads)
+    dom_fn = wl.gemm if not wl.kind.startswith("quant") else wl.step
+    barrier(world)
+    dom_ms = dist_max(timed_loop(dom_fn, args.steps, 3, flush), world, dev) / args.steps
+    if wl.kind.startswith("quant") or name == "c4a":
+        per_launch = (quant_bytes(wl.kind, wl.M, wl.K) if wl.kind.startswith("quant")
+                      else gemm_bytes(wl.kind, wl.batch, wl.M, wl.N, wl.K))
+        achieved = per_launch / 1e9 / (dom_ms / 1e3)
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC.get(name),
+                "peak_source": f"HBM copy bandwidth, {peaks['source']}", "kernel_ms": dom_ms}
+    else:
+        mult = 4.0 if wl.kind == "mxfp4" else 2.0
+        peak = peaks["bf16"] * mult
+        achieved = flops_of(wl.kind, wl.batch, wl.M, wl.N, wl.K) / 1e12 / (dom_ms / 1e3)
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC.get(name), "kernel_ms": dom_ms,
+                "peak_source": f"{mult:g} x dense bf16 cuBLAS burst ({peaks['source']}); "
+                               f"fp8 = 2x, fp4 = 4x the bf16 rate per the datasheet ratios",
+                "frac_of_spec": achieved / (4500.0 if mult == 2.0 else 9000.0)}
+
+    # end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        wl.setup_e2e()
+        barrier(world)
+        e_steps = max(3, min(args.steps, 10))
+        e_ms = dist_max(timed_loop(wl.step_e2e, e_steps, 3, flush), world, dev)
+        e2e = {"value": units * e_steps / (e_ms / 1e3), "unit": unit, "h2d_bytes_per_step": wl.h2d,
+               "d2h_bytes_per_step": wl.d2h, "ms_per_step": e_ms / e_steps}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rows = default_sample_rows(name)
+        cpu_reference_step(name, rows)
+        tot, u_tot, reps = 0.0, 0.0, 0
+        while tot < 10.0 and reps < 8:
+            dt, u, _ = cpu_reference_step(name, rows)
+            tot += dt; u_tot += u; reps += 1
+        kind, B, M, N, K = WORKLOADS[name]
+        cpu = {"value": u_tot / tot, "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{min(M, rows)} of {M} activation rows, {min(N, CPU_SAMPLE_MAX_N)} of {N} weight rows, "
+                         f"all of K={K}, {reps} repetitions"}
+
+    if rank == 0:
+        kind, B, M, N, K = WORKLOADS[name]
+        out = {"metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+               "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+               "vs_baseline": None, "dtype": {"mxfp4": "fp4 (e2m1, e8m0 scales), fp32 accumulate"}.get(
+                   kind, "fp8 (e4m3fn), fp32 accumulate"),
+               "data": "synthetic",
+               "config": {"workload": name, "kind": kind, "batch": B, "M": M, "N": N, "K": K,
+                          "parallelism": f"N-sharded x{world}" if world > 1 else "single GPU",
+                          "step": "dynamic activation quantization + quantized GEMM, weights resident",
+                          "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)"},
+               "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
+               "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

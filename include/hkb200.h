@@ -1,0 +1,113 @@
+/*
+ * hkb200.h -- C ABI of libhkb200.so: the quantized-GEMM path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain DEVICE pointers and sizes, launches asynchronously on the
+ * given CUDA stream (a cudaStream_t passed as void*, NULL = default stream), allocates no
+ * caller-visible memory, and returns 0 on success or a negative hkb_status.  After a
+ * failure hkb_last_error() returns a thread-local message.  Nothing here has a CPU
+ * fallback: without a CUDA device every compute entry point returns HKB_ERR_CUDA.
+ *
+ * Each declaration cites the interface of the reference project (m8than/amd-kernels)
+ * that it replaces, as <path>:<lines> inside that project.
+ */
+#ifndef HKB200_H
+#define HKB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    HKB_OK = 0,
+    HKB_ERR_BAD_ARG = -1,     /* null pointer, bad enum value */
+    HKB_ERR_BAD_SHAPE = -2,   /* dimension not supported (divisibility, zero, too large) */
+    HKB_ERR_BAD_ALIGN = -3,   /* pointer or pitch not aligned as required */
+    HKB_ERR_UNSUPPORTED = -4, /* combination not implemented */
+    HKB_ERR_CUDA = -5,        /* CUDA runtime / driver error, message has the detail */
+    HKB_ERR_TIMEOUT = -6      /* a bounded device-side wait gave up (see hkb_check_status) */
+} hkb_status;
+
+#define HKB_MXFP4_MODE_DOC 0    /* e = floor(log2 amax) - 2, nearest value, ties to smaller */
+#define HKB_MXFP4_MODE_KERNEL 1 /* the reference device code's variant (rounded amax, truncation) */
+
+/* ---- library ------------------------------------------------------------------------- */
+int hkb_version(void);
+const char* hkb_last_error(void);
+/* Frees the per-device workspace (scale re-layout scratch, split-K partials, status word). */
+int hkb_release(void);
+/* Synchronises `stream` and returns HKB_ERR_TIMEOUT if any GEMM launched so far on the
+ * current device abandoned a bounded wait (it then left its output incomplete). */
+int hkb_check_status(void* stream);
+
+/* ---- quantizers ---------------------------------------------------------------------- */
+
+/* Per-row dynamic FP8: scales[m] = max(amax_m / 448, 1e-10), q = e4m3fn(clamp(x / scale)).
+ * x bf16 [M, D] with row pitch ldx elements; q u8 [M, D]; scales f32 [M].  D % 8 == 0.
+ * Replaces per_token_quant_fwd(input, output, scales):
+ *   kernels/quantization/quant/kernel.cpp:31-109,159-171 (re-targeted from INT8/127 to e4m3fn/448). */
+int hkb_quant_fp8_per_token(const void* x, void* q, float* scales,
+                            int64_t M, int64_t D, int64_t ldx, void* stream);
+
+/* The reference kernel's own INT8 mode: scale = max(amax/127, 1e-10), q = rint(x/scale) in [-127,127].
+ *   kernels/quantization/quant/kernel.cpp:92-107. */
+int hkb_quant_int8_per_token(const void* x, void* q, float* scales,
+                             int64_t M, int64_t D, int64_t ldx, void* stream);
+
+/* 1x128 block FP8: one fp32 scale per 128 contiguous columns, scales f32 [M, D/128].
+ * w (bf16 [D]) non-null selects the fused RMSNorm prologue y = x*rsqrt(mean x^2+eps)*w.
+ * Replaces fused_rmsnorm_fp8_quant_fwd(input, weight, output, scales, eps):
+ *   kernels/quantization/fused_fp8_quant/kernel.cpp:110-210,262-275. */
+int hkb_quant_fp8_1x128(const void* x, const void* w_or_null, void* q, float* scales,
+                        int64_t M, int64_t D, float eps, void* stream);
+
+/* 128x128 block FP8 for weights: w bf16 [N, K] -> q u8 [N, K], scales f32 [K/128, N/128]
+ * (transposed, the b_scale layout of the block-scale GEMM).  No reference kernel; produces
+ * the operand layout of kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:7,41,146. */
+int hkb_quant_fp8_128x128(const void* w, void* q, float* scales,
+                          int64_t N, int64_t K, void* stream);
+
+/* MXFP4: e2m1 codes packed 2/byte (element 2i in the low nibble), one e8m0 byte per 32
+ * contiguous elements.  codes u8 [M, D/2], scales u8 [M, D/32].  D % 32 == 0.
+ * Replaces fused_rmsnorm_mxfp4_quant_fwd(input, weight, output, scales, eps):
+ *   kernels/quantization/fused_mxfp4_quant/kernel.cpp:71-169,172-249,301-314. */
+int hkb_quant_mxfp4(const void* x, const void* w_or_null, void* codes, void* scales,
+                    int64_t M, int64_t D, float eps, int mode, void* stream);
+
+/* ---- GEMMs (all "NT": A [M,K] and B [N,K] are K-contiguous; C [M,N] bf16) ------------- */
+
+/* C[b] = bf16( (A[b] @ B[b]^T) * sa[b][m] * sb[b][n] + bias[b][n] ), e4m3fn operands.
+ * batch >= 1; tensors of consecutive batches are contiguous; bias (bf16 [batch, N]) may be NULL.
+ * K % 128 == 0, N % 8 == 0.  Replaces
+ *   gemm_a8w8_per_token_scale_tk.dispatch(A,B,C,a_scale,b_scale)
+ *       kernels/gemm-basic/gemm_a8w8_per_token_scale/kernel.cpp:49-171
+ *   gemm_a8w8_tk.dispatch(A,B,a_scale,b_scale,C)   kernels/gemm-basic/gemm_a8w8/kernel.cpp:46-175
+ *   batched_gemm_a8w8_tk.dispatch(A,B,a_scale,b_scale,C,bias)
+ *       kernels/gemm-batched/batched_gemm_a8w8/kernel.cpp:59-203 */
+int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, const float* sb,
+                     const void* bias_or_null, int64_t batch, int64_t M, int64_t N, int64_t K,
+                     void* stream);
+
+/* C = bf16( sum_kb (A_kb @ B_kb^T) * sa[m, kb] * sb[kb, n / gn] ), e4m3fn operands,
+ * sa f32 [M, K/128], sb f32 [K/128, N/gn], gn in {1, 128}.  K % 128 == 0, N % 128 == 0.
+ * Replaces gemm_a8w8_blockscale_tk.dispatch(A,B,C,a_scale,b_scale):
+ *   kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:51-180. */
+int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* sa,
+                            const float* sb, int64_t gn, int64_t M, int64_t N, int64_t K,
+                            void* stream);
+
+/* C[b] = bf16( dq(A[b]) @ dq(B[b])^T ), dq(v)[i,k] = e2m1(v[i,k]) * 2^(s[i,k/32]-127).
+ * A u8 [batch, M, K/2], B u8 [batch, N, K/2], sfa u8 [batch, M, K/32], sfb u8 [batch, N, K/32].
+ * K % 128 == 0, N % 8 == 0.  Uses library-owned scratch for the scale re-layout.  Replaces
+ *   gemm_afp4wfp4_tk.dispatch           kernels/gemm-basic/gemm_afp4wfp4/kernel.cpp:1-12,48-159
+ *   batched_gemm_afp4wfp4_tk.dispatch   kernels/gemm-batched/batched_gemm_afp4wfp4/kernel.cpp:3-7,52-168
+ * (operand spec from those files' header comments; the reference kernels themselves take
+ * host-dequantized bf16). */
+int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                   int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HKB200_H */

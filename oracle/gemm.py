@@ -1,0 +1,97 @@
+"""CPU oracle for the quantized GEMMs: dequantize, then matmul in fp32 (torch CPU).
+TEST INFRASTRUCTURE (see package docstring).
+
+Expressions followed:
+  per-token   tests/test_gemm.py:183; kernels/gemm-basic/gemm_a8w8_per_token_scale/test_parity.py:45-46
+  block-scale tests/test_gemm.py:148-153; kernels/gemm-basic/gemm_a8w8_blockscale/test_parity.py:57-76
+  mxfp4       kernels/gemm-basic/gemm_afp4wfp4/test_parity.py:30-31 on operands dequantized as
+              kernels/moe-gemm/moe_op_mxfp4/test_parity.py:36-46
+  batched     tests/test_gemm.py:366-367 (bias added in fp32 before the bf16 store)
+  metric      tests/test_gemm.py:190-192
+"""
+import numpy as np
+import torch
+
+from .codecs import e4m3fn_to_f32, e8m0_to_f32, unpack_e2m1
+
+
+def _t(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
+
+
+def _codes(a):
+    if hasattr(a, "detach"):
+        a = a.detach().cpu()
+        if a.dtype != torch.uint8:
+            a = a.view(torch.uint8)
+        a = a.numpy()
+    return np.asarray(a, dtype=np.uint8)
+
+
+def _f32(a):
+    if hasattr(a, "detach"):
+        a = a.detach().cpu().float().numpy()
+    return np.asarray(a, dtype=np.float32)
+
+
+def gemm_fp8_per_token(Aq, Bq, sa, sb, bias=None):
+    """Per-token-scale GEMM on e4m3fn code bytes (see gemm_per_token_f32)."""
+    return gemm_per_token_f32(e4m3fn_to_f32(_codes(Aq)), e4m3fn_to_f32(_codes(Bq)), sa, sb, bias)
+
+
+def gemm_per_token_f32(A, B, sa, sb, bias=None):
+    """C[m,n] = (sum_k A[m,k] B[n,k]) * sa[m] * sb[n] (+ bias[n]) on already-decoded operand
+    values; fp32 result [.., M, N].  Leading batch dimensions broadcast through torch.matmul."""
+    A = _t(_f32(A))
+    B = _t(_f32(B))
+    sa = _t(_f32(sa)).reshape(*A.shape[:-1], 1)
+    sb = _t(_f32(sb)).reshape(*B.shape[:-2], 1, B.shape[-2])
+    C = (A @ B.transpose(-1, -2)) * sa * sb
+    if bias is not None:
+        C = C + _t(_f32(bias)).reshape(*B.shape[:-2], 1, B.shape[-2])
+    return C.numpy()
+
+
+def gemm_fp8_blockscale(Aq, Bq, sa, sb, group_k=128):
+    """Block-scale GEMM on e4m3fn code bytes (see gemm_blockscale_f32)."""
+    return gemm_blockscale_f32(e4m3fn_to_f32(_codes(Aq)), e4m3fn_to_f32(_codes(Bq)), sa, sb, group_k)
+
+
+def gemm_blockscale_f32(A, B, sa, sb, group_k=128):
+    """C = sum_kb (A_kb @ B_kb^T) * sa[:, kb, None] * expand(sb[kb, :]) on decoded operand values;
+    sa [M, K/128], sb [K/128, N/gn] with gn = N / sb.shape[1]."""
+    A = _t(_f32(A))
+    B = _t(_f32(B))
+    sa = _t(_f32(sa))
+    sb = _t(_f32(sb))
+    M, K = A.shape
+    N = B.shape[0]
+    gn = N // sb.shape[1]
+    C = torch.zeros(M, N, dtype=torch.float32)
+    for kg in range(K // group_k):
+        ks = slice(kg * group_k, (kg + 1) * group_k)
+        partial = A[:, ks] @ B[:, ks].T
+        b_s = sb[kg].repeat_interleave(gn)[:N]
+        C += partial * sa[:, kg, None] * b_s[None, :]
+    return C.numpy()
+
+
+def dequant_mxfp4(codes, scale_bytes):
+    """[.., R, K/2] packed e2m1 + [.., R, K/32] e8m0 -> fp32 [.., R, K]."""
+    v = unpack_e2m1(_codes(codes))
+    s = e8m0_to_f32(_codes(scale_bytes))
+    return (v.reshape(*s.shape, 32) * s[..., None]).reshape(v.shape).astype(np.float32)
+
+
+def gemm_mxfp4(Aq, Bq, sfa, sfb):
+    """C = dq(A) @ dq(B)^T in fp32; batch dimensions broadcast."""
+    A = _t(dequant_mxfp4(Aq, sfa))
+    B = _t(dequant_mxfp4(Bq, sfb))
+    return (A @ B.transpose(-1, -2)).numpy()
+
+
+def rel_err(C, C_ref):
+    """max |C - C_ref| / (max |C_ref| + 1e-8), both fp32 (tests/test_gemm.py:190-192)."""
+    C = _f32(C).astype(np.float64)
+    R = _f32(C_ref).astype(np.float64)
+    return float(np.abs(C - R).max() / (np.abs(R).max() + 1e-8))

@@ -1,0 +1,301 @@
+"""GPU tier: the tcgen05 GEMMs against the CPU oracle (dequantize-then-matmul in fp32),
+through the reference-facing `hipkittens` modules.  Tolerance, as stated for this path:
+max|C - C_ref| / max|C_ref| <= 1e-2 with both sides in fp32 (tests/test_gemm.py:190-192 of the
+reference uses the same metric with looser bars)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import codecs, gemm, inputs, quant
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+
+
+def _report(C, ref, what):
+    """Error summary that localises layout bugs: worst element, per-128x128-block maxima."""
+    C = np.asarray(C, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    err = np.abs(C - ref)
+    denom = np.abs(ref).max() + 1e-8
+    idx = np.unravel_index(err.argmax(), err.shape)
+    msg = [f"{what}: rel_err={err.max() / denom:.4g} worst at {idx}: got {C[idx]:.6g} want {ref[idx]:.6g}; "
+           f"nan={np.isnan(C).sum()} zeros={int((C == 0).sum())}/{C.size}"]
+    e2 = err.reshape(-1, err.shape[-2], err.shape[-1])[0]
+    bm, bn = min(128, e2.shape[0]), min(128, e2.shape[1])
+    blocks = [[e2[i:i + bm, j:j + bn].max() / denom for j in range(0, min(e2.shape[1], 1024), bn)]
+              for i in range(0, min(e2.shape[0], 1024), bm)]
+    msg.append("block maxima (rows=M blocks, cols=N blocks): " +
+               "; ".join(" ".join(f"{v:.2g}" for v in row) for row in blocks))
+    rows_bad = np.where((e2 / denom > TOL).any(axis=1))[0]
+    cols_bad = np.where((e2 / denom > TOL).any(axis=0))[0]
+    msg.append(f"bad rows {rows_bad[:16]} (n={len(rows_bad)}), bad cols {cols_bad[:16]} (n={len(cols_bad)})")
+    return "\n".join(msg)
+
+
+def _check(C, ref, what, tol=TOL):
+    C = C.float().cpu().numpy() if hasattr(C, "cpu") else C
+    r = gemm.rel_err(C, ref)
+    assert r <= tol, _report(C, ref, what)
+    return r
+
+
+def _status_ok():
+    import ctypes
+    lib = ctypes.CDLL(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                   "amd-kernels_b200", "kernels", "libhkb200.so"))
+    lib.hkb_last_error.restype = ctypes.c_char_p
+    rc = lib.hkb_check_status(None)
+    assert rc == 0, lib.hkb_last_error().decode()
+
+
+def _fp8_operands(M, N, K, batch=1, seed=42):
+    """e4m3fn-representable operands with the reference tests' scale distributions
+    (rand*0.1+0.01, tests/test_gemm.py:179-180): randn -> per-row quantize."""
+    g = torch.Generator().manual_seed(seed)
+    shape_a = (batch, M, K) if batch > 1 else (M, K)
+    shape_b = (batch, N, K) if batch > 1 else (N, K)
+    A = torch.randn(shape_a, generator=g).bfloat16()
+    B = torch.randn(shape_b, generator=g).bfloat16()
+    aq, _ = quant.quant_fp8_per_token(A.reshape(-1, K))
+    bq, _ = quant.quant_fp8_per_token(B.reshape(-1, K))
+    sa = (torch.rand(shape_a[:-1], generator=g) * 0.1 + 0.01).float()
+    sb = (torch.rand(shape_b[:-1], generator=g) * 0.1 + 0.01).float()
+    return aq.reshape(shape_a), bq.reshape(shape_b), sa, sb
+
+
+def _dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else a
+    t = t.to(DEV)
+    return t.view(dtype) if dtype is not None else t
+
+
+# ---- per-token / per-channel scales ------------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (512, 512, 512), (2048, 2048, 2048),   # the reference's sizes
+                                   (128, 1024, 1024), (200, 1032, 384), (16, 2048, 1024), (1, 256, 128),
+                                   (384, 4608, 512)])
+def test_gemm_per_token_scale(hk, shape):
+    M, N, K = shape
+    aq, bq, sa, sb = _fp8_operands(M, N, K)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(_dev(aq), _dev(bq), C, _dev(sa), _dev(sb))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C, gemm.gemm_fp8_per_token(aq, bq, sa, sb), f"per-token {shape}")
+
+
+def test_gemm_a8w8_module_takes_scales_before_C(hk):
+    aq, bq, sa, sb = _fp8_operands(256, 256, 256)
+    C = torch.zeros(256, 256, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8.dispatch(_dev(aq, torch.float8_e4m3fn), _dev(bq, torch.float8_e4m3fn), _dev(sa), _dev(sb), C)
+    torch.cuda.synchronize()
+    _check(C, gemm.gemm_fp8_per_token(aq, bq, sa, sb), "a8w8 order")
+
+
+def test_config1_quantize_then_gemm_end_to_end(hk):
+    """Config 1: A [128,1024] ~N(0,1), W [1024,1024] ~N(0,0.02), both quantized per row on the
+    GPU, GEMM on the GPU; everything compared with the oracle on the same inputs."""
+    A, W = inputs.make_config("c1")
+    M, K = A.shape
+    N = W.shape[0]
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, 1, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(N, 1, device=DEV)
+    hk.per_token_quant_fwd(A.to(DEV), aq, sa)
+    hk.per_token_quant_fwd(W.to(DEV), wq, sw)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(aq, wq, C, sa, sw)
+    torch.cuda.synchronize()
+    raq, rsa = quant.quant_fp8_per_token(A)
+    rwq, rsw = quant.quant_fp8_per_token(W)
+    assert np.array_equal(aq.cpu().numpy(), raq) and np.array_equal(wq.cpu().numpy(), rwq)
+    Adq = torch.from_numpy(codecs.e4m3fn_to_f32(raq) * rsa)
+    Wdq = torch.from_numpy(codecs.e4m3fn_to_f32(rwq) * rsw)
+    _check(C, (Adq @ Wdq.T).numpy(), "config 1 vs (Aq*sa)(Wq*sw)^T")
+
+
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_batched_gemm_a8w8(hk, with_bias):
+    """B=4, 128^3 as in tests/test_gemm.py:349-390 of the reference, 4-D tensors with a leading 1."""
+    Bn, M, N, K = 4, 128, 128, 128
+    aq, bq, sa, sb = _fp8_operands(M, N, K, batch=Bn)
+    bias = (torch.randn(Bn, N, generator=torch.Generator().manual_seed(5))).bfloat16() if with_bias else None
+    C = torch.zeros(1, Bn, M, N, dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.a8w8.dispatch(_dev(aq).view(1, Bn, M, K), _dev(bq).view(1, Bn, N, K), _dev(sa).view(1, Bn, 1, M),
+                                  _dev(sb).view(1, Bn, 1, N), C, None if bias is None else _dev(bias).view(1, Bn, 1, N))
+    torch.cuda.synchronize()
+    ref = gemm.gemm_fp8_per_token(aq, bq, sa, sb, None if bias is None else bias.float().numpy())
+    _check(C[0], ref, f"batched bias={with_bias}")
+
+
+def test_batched_gemm_ragged_sizes(hk):
+    Bn, M, N, K = 3, 200, 264, 256
+    aq, bq, sa, sb = _fp8_operands(M, N, K, batch=Bn)
+    C = torch.zeros(Bn, M, N, dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.a8w8.dispatch(_dev(aq), _dev(bq), _dev(sa), _dev(sb), C)
+    torch.cuda.synchronize()
+    _check(C, gemm.gemm_fp8_per_token(aq, bq, sa, sb), "batched ragged")
+
+
+def test_reference_golden_shapes_with_int_valued_operands(hk, golden_dir):
+    """The reference's own case (int8 values, seed 42) restricted to values e4m3 holds exactly:
+    operands are clamped to [-16, 16], where every integer is an e4m3 value, so the GEMM must
+    reproduce the oracle's exact-integer accumulation."""
+    g = np.load(os.path.join(golden_dir, "gemm_per_token_128x128x128.npz"))
+    A = np.clip(g["A"], -16, 16).astype(np.float32)
+    B = np.clip(g["B"], -16, 16).astype(np.float32)
+    aq, bq = codecs.f32_to_e4m3fn(A), codecs.f32_to_e4m3fn(B)
+    assert np.array_equal(codecs.e4m3fn_to_f32(aq), A)
+    C = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(_dev(aq), _dev(bq), C, _dev(g["a_scale"]), _dev(g["b_scale"]))
+    ref = torch.from_numpy(gemm.gemm_per_token_f32(A, B, g["a_scale"], g["b_scale"])).bfloat16()
+    assert torch.equal(C.cpu(), ref), _report(C.float().cpu().numpy(), ref.float().numpy(), "int-valued golden")
+
+
+def test_decode_shape_sampled_columns(hk):
+    """Config 4a: M=16, N=28672, K=8192.  The oracle checks 1024 sampled output columns."""
+    M, N, K = 16, 28672, 8192
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, 1, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(N, 1, device=DEV)
+    hk.per_token_quant_fwd(A, aq, sa)
+    hk.per_token_quant_fwd(W, wq, sw)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(aq, wq, C, sa, sw)
+    torch.cuda.synchronize()
+    _status_ok()
+    cols = torch.randperm(N, generator=torch.Generator().manual_seed(0))[:1024].sort().values
+    ref = gemm.gemm_fp8_per_token(aq.cpu(), wq[cols.to(DEV)].cpu(), sa.cpu(), sw[cols.to(DEV)].cpu())
+    _check(C[:, cols.to(DEV)], ref, "decode sampled columns")
+
+
+# ---- block scales ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("shape,gn", [((128, 128, 256), 1), ((128, 128, 128), 128), ((256, 256, 512), 128),
+                                      ((512, 512, 512), 1), ((200, 384, 1024), 128), ((1024, 4096, 2048), 128)])
+def test_gemm_blockscale_reference_scale_distribution(hk, shape, gn):
+    """Shapes and scale distributions of the reference (tests/test_gemm.py:128-162: 128x128x256, gn=1;
+    per-directory reference with generic gn), operands e4m3-representable."""
+    M, N, K = shape
+    aq, bq, _, _ = _fp8_operands(M, N, K)
+    g = torch.Generator().manual_seed(7)
+    sa = torch.rand(M, K // 128, generator=g) * 0.1 + 0.01
+    sb = torch.rand(K // 128, N // gn, generator=g) * 0.1 + 0.01
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(_dev(aq), _dev(bq), C, _dev(sa), _dev(sb))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C, gemm.gemm_fp8_blockscale(aq, bq, sa, sb), f"blockscale {shape} gn={gn}")
+
+
+def test_config2_shrunk_quantize_then_blockscale_gemm(hk):
+    """Config 2 distributions (outlier channels x20, 1x128 / 128x128 scales) at M=512, N=2048, K=4096:
+    quantizers and GEMM on the GPU, oracle on the same inputs."""
+    A, W = inputs.make_inputs(512, 2048, 4096, outliers=True)
+    M, K = A.shape
+    N = W.shape[0]
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, K // 128, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(K // 128, N // 128, device=DEV)
+    hk.fused_rmsnorm_fp8_quant_fwd(A.to(DEV), None, aq, sa, 1e-6)
+    hk.weight_quant_128x128(W.to(DEV), wq, sw)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(aq, wq, C, sa, sw)
+    torch.cuda.synchronize()
+    raq, rsa = quant.quant_fp8_1x128(A)
+    rwq, rsw = quant.quant_fp8_128x128(W)
+    assert np.array_equal(aq.cpu().numpy(), raq) and np.array_equal(wq.cpu().numpy(), rwq)
+    ref = gemm.gemm_fp8_blockscale(raq, rwq, rsa, rsw)
+    _check(C, ref, "config 2 (shrunk)")
+    # quantization error against the unquantized bf16 product stays small despite the outliers
+    assert gemm.rel_err(C.float().cpu().numpy(), (A.float() @ W.float().T).numpy()) < 0.05
+
+
+def test_config2_full_size_sampled_rows(hk):
+    """Config 2 at full size (4096 x 14336 x 4096); the oracle checks 96 sampled rows of C."""
+    M, N, K = 4096, 14336, 4096
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    idx = torch.randperm(K, generator=torch.Generator().manual_seed(42))[:41].to(DEV)
+    A[:, idx] = (A[:, idx].float() * 20).bfloat16()
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, K // 128, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(K // 128, N // 128, device=DEV)
+    hk.fused_rmsnorm_fp8_quant_fwd(A, None, aq, sa, 1e-6)
+    hk.weight_quant_128x128(W, wq, sw)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(aq, wq, C, sa, sw)
+    torch.cuda.synchronize()
+    _status_ok()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:96].sort().values.to(DEV)
+    ref = gemm.gemm_fp8_blockscale(aq[rows].cpu(), wq.cpu(), sa[rows].cpu(), sw.cpu())
+    _check(C[rows], ref, "config 2 full size, sampled rows")
+
+
+# ---- MXFP4 ----------------------------------------------------------------------------------------
+
+def _mxfp4_operands(M, N, K, batch=1, seed=42):
+    g = torch.Generator().manual_seed(seed)
+    sa = (batch, M, K) if batch > 1 else (M, K)
+    sb = (batch, N, K) if batch > 1 else (N, K)
+    A = torch.randn(sa, generator=g).bfloat16()
+    W = (torch.randn(sb, generator=g) * 0.02).bfloat16()
+    ac, asc = quant.quant_mxfp4(A.reshape(-1, K))
+    wc, wsc = quant.quant_mxfp4(W.reshape(-1, K))
+    return (ac.reshape(*sa[:-1], K // 2), wc.reshape(*sb[:-1], K // 2),
+            asc.reshape(*sa[:-1], K // 32), wsc.reshape(*sb[:-1], K // 32))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (128, 128, 128), (256, 256, 256), (1024, 1024, 1024),
+                                   (200, 264, 512), (128, 128, 384), (512, 2048, 8192)])
+def test_gemm_mxfp4(hk, shape):
+    M, N, K = shape
+    ac, wc, asc, wsc = _mxfp4_operands(M, N, K)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.afp4wfp4.dispatch(_dev(ac), _dev(wc), C, _dev(asc), _dev(wsc))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C, gemm.gemm_mxfp4(ac, wc, asc, wsc), f"mxfp4 {shape}")
+
+
+def test_gemm_mxfp4_rejects_host_dequantized_form(hk):
+    x = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="packed e2m1"):
+        hk.gemm.afp4wfp4.dispatch(x, x, x)
+
+
+def test_batched_gemm_mxfp4_reference_golden(hk, golden_dir):
+    """The reference's batched FP4 case (B=4, 128^3, seed 42; kernels/gemm-batched/
+    batched_gemm_afp4wfp4/test_parity.py:27-63) as packed codes + e8m0 bytes."""
+    g = np.load(os.path.join(golden_dir, "gemm_afp4_batched.npz"))
+    Bn, M, _ = g["A"].shape
+    N = g["B"].shape[1]
+    C = torch.zeros(1, Bn, M, N, dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.afp4wfp4.dispatch(_dev(g["A"]), _dev(g["B"]), C, _dev(g["a_scales"]), _dev(g["b_scales"]))
+    torch.cuda.synchronize()
+    ref = torch.from_numpy(g["C_bf16"].view(np.int16).copy()).view(torch.bfloat16).float().numpy()
+    _check(C[0], ref, "batched mxfp4 golden")
+
+
+def test_config3_quantize_then_mxfp4_gemm_sampled(hk):
+    """Config 3 distributions at 2048 x 8192 x 8192: MXFP4 quantizers and GEMM on the GPU; the oracle
+    re-derives 128 sampled rows from the GPU codes (which are themselves checked bit-exact elsewhere)."""
+    M, N, K = 2048, 8192, 8192
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    ac = torch.empty(M, K // 2, dtype=torch.uint8, device=DEV); asc = torch.empty(M, K // 32, dtype=torch.uint8, device=DEV)
+    wc = torch.empty(N, K // 2, dtype=torch.uint8, device=DEV); wsc = torch.empty(N, K // 32, dtype=torch.uint8, device=DEV)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, ac, asc, 1e-6)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, wc, wsc, 1e-6)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.afp4wfp4.dispatch(ac, wc, C, asc, wsc)
+    torch.cuda.synchronize()
+    _status_ok()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(2))[:128].sort().values.to(DEV)
+    ref = gemm.gemm_mxfp4(ac[rows].cpu(), wc.cpu(), asc[rows].cpu(), wsc.cpu())
+    _check(C[rows], ref, "config 3 (M=2048) sampled rows")

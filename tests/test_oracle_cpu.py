@@ -1,0 +1,185 @@
+"""CPU tier: pins the oracle against the golden vectors made from the reference project's own
+Python reference code (tests/golden/make_golden.py) and against torch's casts."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import codecs, gemm, inputs, quant
+
+
+def _bf16_from_bits(bits):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+# ---- codecs --------------------------------------------------------------------------------
+
+def test_e4m3_cast_matches_torch_on_every_bf16_value():
+    x = (np.arange(65536, dtype=np.uint32) << 16).view(np.float32)
+    ok = ~np.isnan(x)
+    ref = torch.from_numpy(x.copy()).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    got = codecs.f32_to_e4m3fn(np.clip(x, -448, 448))
+    assert np.array_equal(ref[ok], got[ok])
+
+
+def test_e4m3_cast_matches_torch_on_random_fp32_and_ties():
+    rng = np.random.default_rng(1)
+    y = rng.standard_normal(1_000_000).astype(np.float32) * np.exp(rng.uniform(-14, 7, 1_000_000)).astype(np.float32)
+    ties = (codecs.E4M3_TABLE[:126] + codecs.E4M3_TABLE[1:127]) / 2      # exact midpoints between codes
+    y = np.concatenate([y, ties, -ties, np.float32([0.0, -0.0, 448, 463.99, 464, 1e9, -1e9, np.inf])])
+    ref = torch.from_numpy(y).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(ref, codecs.f32_to_e4m3fn(y))
+
+
+def test_e4m3_decode_matches_torch():
+    c = np.arange(256, dtype=np.uint8)
+    ref = torch.from_numpy(c).view(torch.float8_e4m3fn).float().numpy()
+    got = codecs.e4m3fn_to_f32(c)
+    assert np.array_equal(np.isnan(ref), np.isnan(got))
+    assert np.array_equal(ref[~np.isnan(ref)], got[~np.isnan(got)])
+
+
+def test_e2m1_lut_nibble_order_and_e8m0_decode_match_reference(golden_dir):
+    g = _load(golden_dir, "e2m1_lut.npz")
+    assert np.array_equal(g["lut"], codecs.E2M1_LUT)
+    allb = np.arange(256, dtype=np.uint8)
+    un = codecs.unpack_e2m1(allb[:, None])
+    assert np.array_equal(un[:, 0], g["lo"]) and np.array_equal(un[:, 1], g["hi"])
+    assert np.array_equal(codecs.e8m0_to_f32(allb)[1:255], g["e8m0"])
+    assert codecs.e8m0_to_f32(np.uint8(0)) == 0.0           # reference decoder: byte 0 -> 0.0
+    assert np.array_equal(codecs.pack_e2m1(np.array([[1, 10, 7, 15]])), np.array([[0xA1, 0xF7]], dtype=np.uint8))
+
+
+# ---- quantizers ----------------------------------------------------------------------------
+
+def test_static_fp8_cast_golden(golden_dir):
+    g = _load(golden_dir, "quant_static_fp8.npz")
+    x = _bf16_from_bits(g["x_bf16"]).float().numpy()
+    got = codecs.f32_to_e4m3fn(np.clip(x / np.float32(0.5), -448, 448))
+    assert np.array_equal(got, g["bytes"])
+
+
+def test_int8_per_token_golden(golden_dir):
+    g = _load(golden_dir, "quant_int8_per_token.npz")
+    q, s = quant.quant_int8_per_token(_bf16_from_bits(g["x_bf16"]))
+    assert np.array_equal(s, g["scales"])
+    assert np.array_equal(q, g["q"])
+
+
+@pytest.mark.parametrize("shape", [(128, 1024), (16, 8192), (3, 136)])
+def test_fp8_per_token_equals_reference_expression(shape):
+    x = torch.randn(shape, generator=torch.Generator().manual_seed(42)).bfloat16()
+    x[0, :5] = torch.tensor([0.0, -0.0, 1e-30, -1e-30, 3e38]).bfloat16()
+    xf = x.float()
+    amax = xf.abs().amax(1, keepdim=True)
+    scale = (amax / 448.0).clamp(min=1e-10)
+    ref = (xf / scale).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    q, s = quant.quant_fp8_per_token(x)
+    assert np.array_equal(s, scale.numpy())
+    assert np.array_equal(q, ref)
+
+
+def test_fp8_1x128_and_128x128_equal_blockwise_expression():
+    A, W = inputs.make_inputs(64, 256, 512, outliers=True)
+    q, s = quant.quant_fp8_1x128(A)
+    xf = A.float().reshape(64, 4, 128)
+    sc = (xf.abs().amax(2, keepdim=True) / 448.0).clamp(min=1e-10)
+    ref = (xf / sc).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).reshape(64, 512).numpy()
+    assert np.array_equal(q, ref) and np.array_equal(s, sc.reshape(64, 4).numpy())
+    qw, sw = quant.quant_fp8_128x128(W)
+    assert sw.shape == (4, 2)                                 # [K/128, N/128], transposed
+    wf = W.float()
+    for nb in range(2):
+        for kb in range(4):
+            t = wf[nb * 128:(nb + 1) * 128, kb * 128:(kb + 1) * 128]
+            sc = max(t.abs().max().item() / 448.0, 1e-10)
+            assert sw[kb, nb] == np.float32(np.float32(t.abs().max().item()) / np.float32(448.0))
+            ref = (t / np.float32(sc)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+            assert np.array_equal(qw[nb * 128:(nb + 1) * 128, kb * 128:(kb + 1) * 128], ref)
+
+
+def test_all_zero_rows_use_the_scale_floor():
+    x = torch.zeros(2, 128).bfloat16()
+    q, s = quant.quant_fp8_per_token(x)
+    assert np.all(s == np.float32(1e-10)) and np.all(q == 0)
+    codes, sb = quant.quant_mxfp4(torch.zeros(1, 64).bfloat16())
+    assert np.all(codes == 0) and np.all(sb == 0)
+
+
+def test_mxfp4_vectorised_equals_reference_text_loop():
+    x = torch.randn(8, 256, generator=torch.Generator().manual_seed(42)).bfloat16()
+    # exact ties and saturation inside one block whose amax is 6 -> e = 0
+    x[0, :10] = torch.tensor([6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -5.0]).bfloat16()
+    x[0, 10:32] = 0
+    packed, sb = quant.quant_mxfp4(x)
+    dq = codecs.unpack_e2m1(packed)
+    for r in range(8):
+        vals, scales = quant.quant_mxfp4_literal(x[r].float().numpy())
+        assert np.array_equal(vals, dq[r]) and np.array_equal(scales, sb[r])
+    assert sb[0, 0] == 127
+    assert list(dq[0, :10]) == [6.0, 0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, -0.0, -4.0]
+
+
+def test_mxfp4_modes_differ_as_documented():
+    x = torch.randn(64, 1024, generator=torch.Generator().manual_seed(42)).bfloat16()
+    p0, s0 = quant.quant_mxfp4(x, mode=quant.MODE_DOC)
+    p1, s1 = quant.quant_mxfp4(x, mode=quant.MODE_KERNEL)
+    frac = (s0 != s1).mean()
+    assert 0.05 < frac < 0.3          # the reference's two definitions disagree on ~16 % of scale bytes
+    # kernel mode rounds amax up when its mantissa is >= 1.75: exponents only ever grow
+    assert np.all(s1.astype(int) - s0.astype(int) >= 0)
+
+
+# ---- GEMM expressions against the reference's own reference functions --------------------------
+
+@pytest.mark.parametrize("name", ["gemm_per_token_128x128x128.npz", "gemm_per_token_512x512x512.npz"])
+def test_gemm_per_token_golden(golden_dir, name):
+    g = _load(golden_dir, name)
+    C = gemm.gemm_per_token_f32(g["A"].astype(np.float32), g["B"].astype(np.float32), g["a_scale"], g["b_scale"])
+    got = torch.from_numpy(C).bfloat16()
+    # int8 operands with K <= 512: every fp32 partial sum is an exact integer, so the result is
+    # independent of the summation order and must match bit for bit
+    assert torch.equal(got, _bf16_from_bits(g["C_bf16"]))
+
+
+@pytest.mark.parametrize("name", ["gemm_blockscale_128x128x256_gn1.npz", "gemm_blockscale_256x256x512_gn128.npz"])
+def test_gemm_blockscale_golden(golden_dir, name):
+    g = _load(golden_dir, name)
+    C = gemm.gemm_blockscale_f32(g["A"].astype(np.float32), g["B"].astype(np.float32), g["a_scale"], g["b_scale"])
+    ref = _bf16_from_bits(g["C_bf16"]).float().numpy()
+    assert gemm.rel_err(torch.from_numpy(C).bfloat16(), ref) < 1e-5 + 2 ** -8   # bf16 rounding of an fp32 sum
+
+
+def test_gemm_mxfp4_batched_golden(golden_dir):
+    g = _load(golden_dir, "gemm_afp4_batched.npz")
+    assert np.array_equal(gemm.dequant_mxfp4(g["A"], g["a_scales"]), g["A_dq"])
+    assert np.array_equal(gemm.dequant_mxfp4(g["B"], g["b_scales"]), g["B_dq"])
+    C = gemm.gemm_mxfp4(g["A"], g["B"], g["a_scales"], g["b_scales"])
+    ref = _bf16_from_bits(g["C_bf16"]).float().numpy()
+    assert gemm.rel_err(torch.from_numpy(C).bfloat16(), ref) < 2 ** -8
+
+
+def test_fp8_gemm_oracle_is_dequantize_then_matmul():
+    A, W = inputs.make_config("c1")
+    aq, sa = quant.quant_fp8_per_token(A)
+    wq, sw = quant.quant_fp8_per_token(W)
+    C = gemm.gemm_fp8_per_token(aq, wq, sa, sw)
+    Adq = torch.from_numpy(codecs.e4m3fn_to_f32(aq) * sa)
+    Wdq = torch.from_numpy(codecs.e4m3fn_to_f32(wq) * sw)
+    assert gemm.rel_err(C, (Adq @ Wdq.T).numpy()) < 1e-5
+    # and quantization error itself is small against the unquantized product
+    assert gemm.rel_err(C, (A.float() @ W.float().T).numpy()) < 0.05
+
+
+def test_inputs_are_reproducible_and_have_outlier_channels():
+    A1, W1 = inputs.make_inputs(256, 128, 4096, outliers=True)
+    A2, W2 = inputs.make_inputs(256, 128, 4096, outliers=True)
+    assert torch.equal(A1, A2) and torch.equal(W1, W2)
+    col_amax = A1.float().abs().amax(0)
+    assert (col_amax > 20).sum().item() >= 30          # 1 % of 4096 channels scaled x20
+    assert abs(W1.float().std().item() - 0.02) < 0.002
