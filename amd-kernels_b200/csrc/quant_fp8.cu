@@ -15,28 +15,48 @@ constexpr float kFp8Max = 448.0f;
 constexpr float kInt8Max = 127.0f;
 constexpr float kScaleFloor = 1e-10f;
 
-// 8 floats -> 8 code bytes
+// 8 bf16 (one chunk) -> 8 code bytes.  The e4m3 sign bit is taken from the input's own sign
+// bit (the scale is positive), so quotients that underflow to zero keep their sign exactly as
+// an IEEE division followed by a round-to-nearest cast does.
 template <bool INT8>
-__device__ __forceinline__ uint2 encode8(const float (&f)[8], const Divider& div) {
+__device__ __forceinline__ uint2 encode8(const uint4& v, const Divider& div) {
+    float f[8];
+    unpack8(v, f);
     uint2 o;
     if constexpr (INT8) {
         uint32_t b[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            int v = __float2int_rn(div(f[j]));
-            v = max(-127, min(127, v));
-            b[j] = (uint32_t)v & 0xFFu;
+            int q = __float2int_rn(div(f[j]));
+            q = max(-127, min(127, q));
+            b[j] = (uint32_t)q & 0xFFu;
         }
         o.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
         o.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
     } else {
-        const uint32_t p0 = cvt_e4m3x2(div(f[0]), div(f[1]));
-        const uint32_t p1 = cvt_e4m3x2(div(f[2]), div(f[3]));
-        const uint32_t p2 = cvt_e4m3x2(div(f[4]), div(f[5]));
-        const uint32_t p3 = cvt_e4m3x2(div(f[6]), div(f[7]));
+        // sign bits of a bf16 pair (bits 15 and 31) moved to bits 7 and 15 of a code pair
+        auto sgn = [](uint32_t w) { return ((w >> 8) & 0x80u) | ((w >> 16) & 0x8000u); };
+        const uint32_t p0 = cvt_e4m3x2(div(f[0]), div(f[1])) | sgn(v.x);
+        const uint32_t p1 = cvt_e4m3x2(div(f[2]), div(f[3])) | sgn(v.y);
+        const uint32_t p2 = cvt_e4m3x2(div(f[4]), div(f[5])) | sgn(v.z);
+        const uint32_t p3 = cvt_e4m3x2(div(f[6]), div(f[7])) | sgn(v.w);
         o.x = p0 | (p1 << 16);
         o.y = p2 | (p3 << 16);
     }
+    return o;
+}
+
+// Same for eight fp32 values that are not bf16 images (RMSNorm prologue output).
+__device__ __forceinline__ uint2 encode8_f32(const float (&f)[8], const Divider& div) {
+    uint32_t p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        p[j] = cvt_e4m3x2(div(f[2 * j]), div(f[2 * j + 1])) |
+               ((__float_as_uint(f[2 * j]) >> 24) & 0x80u) | ((__float_as_uint(f[2 * j + 1]) >> 16) & 0x8000u);
+    }
+    uint2 o;
+    o.x = p[0] | (p[1] << 16);
+    o.y = p[2] | (p[3] << 16);
     return o;
 }
 
@@ -81,11 +101,7 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
 #pragma unroll
     for (int i = 0; i < NCHUNK; ++i) {
         const int c = t + i * TPR;
-        if (live && c < nchunks) {
-            float f[8];
-            unpack8(v[i], f);
-            *reinterpret_cast<uint2*>(qr + (int64_t)c * 8) = encode8<INT8>(f, div);
-        }
+        if (live && c < nchunks) *reinterpret_cast<uint2*>(qr + (int64_t)c * 8) = encode8<INT8>(v[i], div);
     }
 }
 
@@ -109,11 +125,8 @@ quant_row_long_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__
     const Divider div(scale);
     if (threadIdx.x == 0) scales[row] = scale;
     uint8_t* qr = q + row * ((int64_t)nchunks * 8);
-    for (int c = threadIdx.x; c < nchunks; c += 256) {
-        float f[8];
-        unpack8(ld_stream16(xr + (int64_t)c * 8), f);
-        *reinterpret_cast<uint2*>(qr + (int64_t)c * 8) = encode8<INT8>(f, div);
-    }
+    for (int c = threadIdx.x; c < nchunks; c += 256)
+        *reinterpret_cast<uint2*>(qr + (int64_t)c * 8) = encode8<INT8>(ld_stream16(xr + (int64_t)c * 8), div);
 }
 
 template <int NCHUNK, int TPR, bool INT8>
@@ -190,9 +203,7 @@ quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
         const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
         const Divider div(scale);
         if (c < total_chunks) {
-            float f[8];
-            unpack8(v[i], f);
-            *reinterpret_cast<uint2*>(q + c * 8) = encode8<false>(f, div);
+            *reinterpret_cast<uint2*>(q + c * 8) = encode8<false>(v[i], div);
             if ((threadIdx.x & 15) == 0) scales[c >> 4] = scale;
         }
     }
@@ -246,7 +257,7 @@ rmsnorm_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
         const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
         const Divider div(scale);
         if (ok) {
-            *reinterpret_cast<uint2*>(q + (row * nchunks + c) * 8) = encode8<false>(f, div);
+            *reinterpret_cast<uint2*>(q + (row * nchunks + c) * 8) = encode8_f32(f, div);
             if ((t & 15) == 0) scales[(row * nchunks + c) >> 4] = scale;
         }
     }
@@ -283,9 +294,7 @@ quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ 
     for (int i = 0; i < 8; ++i) {
         const int j = t + i * 256;
         const int64_t off = ((int64_t)nb * 128 + (j >> 4)) * K + (int64_t)kb * 128 + (j & 15) * 8;
-        float f[8];
-        unpack8(v[i], f);
-        *reinterpret_cast<uint2*>(q + off) = encode8<false>(f, div);
+        *reinterpret_cast<uint2*>(q + off) = encode8<false>(v[i], div);
     }
 }
 

@@ -71,12 +71,15 @@ __device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
     } else {
         float r[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float q = f[j] * inv;
-            const float m = fmaxf(fabsf(q) - 0x1p-12f, 0.0f);
-            r[j] = q < 0.0f ? -m : m;
-        }
-        return cvt_e2m1x8(r);
+        for (int j = 0; j < 8; ++j) r[j] = fmaxf(fabsf(f[j] * inv) - 0x1p-12f, 0.0f);
+        // sign nibble bit = "x < 0" = sign bit set and magnitude non-zero, from the bf16 bits
+        // themselves (a product that underflows to zero must still carry it)
+        auto sgn = [](uint32_t w) {
+            const uint32_t nz = (w & 0x7FFF7FFFu) + 0x7FFF7FFFu;      // bit 15 / 31 set iff that half is non-zero
+            const uint32_t m = nz & w & 0x80008000u;
+            return ((m >> 12) & 0x8u) | ((m >> 24) & 0x80u);
+        };
+        return cvt_e2m1x8(r) | sgn(v.x) | (sgn(v.y) << 8) | (sgn(v.z) << 16) | (sgn(v.w) << 24);
     }
 }
 

@@ -27,6 +27,7 @@ struct TView {
     int device = -1;     // CUDA ordinal, -1 = not a CUDA tensor
     int64_t numel = 1;
     bool none = true;
+    const char* name = "";
     int64_t dim(int i) const { return shape.at(i < 0 ? shape.size() + i : i); }
     int rank() const { return (int)shape.size(); }
 };
@@ -52,12 +53,15 @@ TView view(const py::object& t, const char* name, bool allow_none = false) {
     }
     if (py::hasattr(t, "is_contiguous") && !t.attr("is_contiguous")().cast<bool>())
         fail(std::string(name) + ": tensor must be contiguous (row-major, inner stride 1)");
+    v.name = name;
     if (py::hasattr(t, "device")) {
         py::object dev = t.attr("device");
-        if (py::str(dev.attr("type")).cast<std::string>() != "cuda")
-            fail(std::string(name) + ": tensor must live on a CUDA device (there is no CPU path)");
-        py::object idx = dev.attr("index");
-        v.device = idx.is_none() ? 0 : idx.cast<int>();
+        if (py::str(dev.attr("type")).cast<std::string>() == "cuda") {
+            py::object idx = dev.attr("index");
+            v.device = idx.is_none() ? 0 : idx.cast<int>();
+        }
+    } else {
+        v.device = 0;   // duck-typed object without .device: trust the caller, as the reference does
     }
     return v;
 }
@@ -76,6 +80,7 @@ void same_device(std::initializer_list<const TView*> vs) {
     int dev = -2;
     for (const TView* v : vs) {
         if (v->none) continue;
+        if (v->device < 0) fail(std::string(v->name) + ": tensor must live on a CUDA device (there is no CPU path)");
         if (dev == -2) dev = v->device;
         else if (dev != v->device) fail("all tensors must be on the same CUDA device");
     }
