@@ -57,7 +57,7 @@ def gemm_a8w8_blockscale(A, Wq_r, C_r, a_scale, b_scale_r, gather=False, group=N
     world = dist.get_world_size(group)
     M, n_local = C_r.shape
     blocked = torch.empty((world, M, n_local), dtype=C_r.dtype, device=C_r.device)
-    dist.all_gather_into_tensor(blocked, C_r.contiguous(), group=group)
+    dist.all_gather_into_tensor(blocked.view(world * M, n_local), C_r.contiguous(), group=group)
     # [g, M, N/g] (what the collective produces) -> [M, N]
     full = blocked.permute(1, 0, 2).reshape(M, world * n_local)
     if out is not None:
