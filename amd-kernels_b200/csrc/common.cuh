@@ -115,6 +115,39 @@ struct Divider {
     }
 };
 
+// bf16 pair -> (lo, hi) as fp32
+__device__ __forceinline__ float2 bf16x2_to_f2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
+// Divider for two values at a time on the packed fp32 pipe (fmul2 / ffma2); same rounding.
+struct Divider2 {
+    float s, r;
+    float2 r2, ns2;
+    bool exact;
+    __device__ __forceinline__ explicit Divider2(float scale) {
+        const Divider d(scale);
+        s = d.s; r = d.r; exact = d.exact;
+        r2 = make_float2(r, r);
+        ns2 = make_float2(-s, -s);
+    }
+    __device__ __forceinline__ float2 operator()(float2 x) const {
+        if (exact) return make_float2(__fdiv_rn(x.x, s), __fdiv_rn(x.y, s));
+        const float2 q0 = __fmul2_rn(x, r2);
+        const float2 e = __ffma2_rn(q0, ns2, x);
+        return __ffma2_rn(e, r2, q0);
+    }
+};
+
+// max |.| over the 8 bf16 of a chunk as a packed bf16 pair (both halves hold partial maxima)
+__device__ __forceinline__ __nv_bfloat162 amax8_packed(const uint4& v) {
+    const uint32_t m = 0x7FFF7FFFu;
+    uint32_t x0 = v.x & m, x1 = v.y & m, x2 = v.z & m, x3 = v.w & m;
+    return __hmax2(__hmax2(*reinterpret_cast<__nv_bfloat162*>(&x0), *reinterpret_cast<__nv_bfloat162*>(&x1)),
+                   __hmax2(*reinterpret_cast<__nv_bfloat162*>(&x2), *reinterpret_cast<__nv_bfloat162*>(&x3)));
+}
+__device__ __forceinline__ float hmax_halves(__nv_bfloat162 m) { return fmaxf(__low2float(m), __high2float(m)); }
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));

@@ -6,6 +6,9 @@
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocator + MMA issuer (one elected lane)
 //   warps 2..   epilogue: TMEM -> registers (tcgen05.ld) -> scale -> bf16 -> global
+//               (block-scale kernels start the epilogue at warp 4, so that the first warpgroup
+//               can hand registers to the epilogue warpgroups, which keep 128 fp32 accumulators
+//               per thread)
 //
 // Two scale schemes share the pipeline:
 //   * per-token / per-channel (kBlockScale = false): the whole K extent accumulates in TMEM
@@ -107,8 +110,15 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N
         if (col0 + j < N) store_bf16x8(crow + col0 + j, v + j);
 }
 
+template <int BN, bool kBlockScale>
+constexpr int gemm_threads() { return (kBlockScale ? 128 : 64) + 128 * (BN == 256 ? 2 : 1); }
+
+__device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, float2 c) {
+    return __ffma2_rn(make_float2(__uint_as_float(a0), __uint_as_float(a1)), s, c);
+}
+
 template <int BN, int STAGES, bool kBlockScale, bool kGn128>
-__global__ void __launch_bounds__(64 + 128 * (BN == 256 ? 2 : 1), 1)
+__global__ void __launch_bounds__(gemm_threads<BN, kBlockScale>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     using L = SmemLayout<BN, STAGES>;
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
@@ -116,6 +126,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     constexpr int COLS_PER_GROUP = BN / EPI_GROUPS;
     constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
     constexpr uint32_t IDESC = idesc_f8(BM, BN);
+    constexpr int EPI_WARP0 = kBlockScale ? 4 : 2;      // first epilogue warp
+    constexpr bool kRegSplit = kBlockScale && BN == 256; // 3 warpgroups: trade registers between them
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -152,6 +164,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (warp < EPI_WARP0) {
+    if constexpr (kRegSplit) reg_dealloc<96>();      // first warpgroup: producer, MMA issuer, two idle warps
     if (warp == 0) {
         // ================= TMA producer =================
         if (elect_one()) {
@@ -218,9 +232,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
+    }
     } else {
         // ================= epilogue =================
-        const int ew = warp - 2;                 // 0 .. EPI_WARPS-1
+        if constexpr (kRegSplit) reg_alloc<184>();   // epilogue warpgroups take the registers WG0 gave up
+        const int ew = warp - EPI_WARP0;         // 0 .. EPI_WARPS-1
         const int quarter = warp & 3;            // TMEM lane quarter this warp may read
         const int grp = ew >> 2;                 // column group
         const int row_in_tile = quarter * 32 + lane;
@@ -265,20 +281,74 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(acc));
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            } else if constexpr (kGn128) {
+                // one scale per (row, K block) and per (K block, 128 columns): a single fp32 factor
+                // per thread and K block.  128 accumulators per thread as 64 float2 (packed FMA).
+                static_assert(COLS_PER_GROUP == 128, "block-scale epilogue groups own 128 columns");
+                float2 acc2[64];
+#pragma unroll
+                for (int j = 0; j < 64; ++j) acc2[j] = make_float2(0.0f, 0.0f);
+                const int kbs = kblocks;
+                const float* sarow = p.sa + (int64_t)(row_ok ? row : p.M - 1) * kbs;
+                const int nsb = p.N / 128;
+                const float* sbcol = p.sb + min(col_base / 128, nsb - 1);
+                float sa_next = __ldg(sarow), sb_next = __ldg(sbcol);
+                for (int kb = 0; kb < kbs; ++kb) {
+                    const float sc = sa_next * sb_next;
+                    const float2 s2 = make_float2(sc, sc);
+                    if (kb + 1 < kbs) {                       // next block's scales arrive under this block's work
+                        sa_next = __ldg(sarow + kb + 1);
+                        sb_next = __ldg(sbcol + (int64_t)(kb + 1) * nsb);
+                    }
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
+                    uint32_t ra[32], rb[32];
+                    tmem_ld32(t_addr, ra);
+                    tmem_ld_wait32(ra);
+                    tmem_ld32(t_addr + 32, rb);               // in flight during the FMAs on ra
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc2[j] = ffma2(ra[2 * j], ra[2 * j + 1], s2, acc2[j]);
+                    tmem_ld_wait32(rb);
+                    tmem_ld32(t_addr + 64, ra);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc2[16 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[16 + j]);
+                    tmem_ld_wait32(ra);
+                    tmem_ld32(t_addr + 96, rb);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc2[32 + j] = ffma2(ra[2 * j], ra[2 * j + 1], s2, acc2[32 + j]);
+                    tmem_ld_wait32(rb);
+                    // the partial product now lives in registers: hand the TMEM buffer back before the last FMAs
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc2[48 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[48 + j]);
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+                if (ok && row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 128; c += 8) {
+                        if (col_base + c < p.N) {
+                            const float v[8] = {acc2[c / 2].x, acc2[c / 2].y, acc2[c / 2 + 1].x, acc2[c / 2 + 1].y,
+                                                acc2[c / 2 + 2].x, acc2[c / 2 + 2].y, acc2[c / 2 + 3].x, acc2[c / 2 + 3].y};
+                            store_bf16x8(crow + col_base + c, v);
+                        }
+                    }
+                }
             } else {
+                // per-column weight scales (gn = 1): secondary mode, plain scalar code
                 float accv[COLS_PER_GROUP];
 #pragma unroll
                 for (int j = 0; j < COLS_PER_GROUP; ++j) accv[j] = 0.0f;
                 const int kbs = kblocks;
                 const float* sarow = p.sa + (int64_t)(row_ok ? row : p.M - 1) * kbs;
-                const int nsb = p.N / p.gn;                       // columns of sb
+                const int nsb = p.N;
                 float sa_next = __ldg(sarow);
                 for (int kb = 0; kb < kbs; ++kb) {
                     const float sa = sa_next;
                     if (kb + 1 < kbs) sa_next = __ldg(sarow + kb + 1);
                     const float* sbrow = p.sb + (int64_t)kb * nsb;
-                    float s_scalar = 0.0f;
-                    if constexpr (kGn128) s_scalar = sa * __ldg(sbrow + min(col_base / 128, nsb - 1));
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
@@ -287,15 +357,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         uint32_t r[32];
                         tmem_ld32(t_addr + c, r);
                         tmem_ld_wait();
-                        if constexpr (kGn128) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) accv[c + j] = __fmaf_rn(__uint_as_float(r[j]), s_scalar, accv[c + j]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int col = min(col_base + c + j, p.N - 1);
-                                accv[c + j] = __fmaf_rn(__uint_as_float(r[j]), sa * __ldg(sbrow + col), accv[c + j]);
-                            }
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = min(col_base + c + j, p.N - 1);
+                            accv[c + j] = __fmaf_rn(__uint_as_float(r[j]), sa * __ldg(sbrow + col), accv[c + j]);
                         }
                     }
                     tc_fence_before();
@@ -336,8 +401,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     const int sms = sm_count();
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
     const int grid = tiles < sms ? tiles : sms;
-    constexpr int threads = 64 + 128 * (BN == 256 ? 2 : 1);
-    kern<<<grid, threads, L::kDynamic, st>>>(tmA, tmB, p);
+    kern<<<grid, gemm_threads<BN, kBlockScale>(), L::kDynamic, st>>>(tmA, tmB, p);
     return check_launch("gemm_fp8_kernel");
 }
 

@@ -19,39 +19,31 @@ constexpr float kScaleFloor = 1e-10f;
 // bit (the scale is positive), so quotients that underflow to zero keep their sign exactly as
 // an IEEE division followed by a round-to-nearest cast does.
 template <bool INT8>
-__device__ __forceinline__ uint2 encode8(const uint4& v, const Divider& div) {
-    float f[8];
-    unpack8(v, f);
+__device__ __forceinline__ uint2 encode8(const uint4& v, const Divider2& div) {
+    const float2 q0 = div(bf16x2_to_f2(v.x));
+    const float2 q1 = div(bf16x2_to_f2(v.y));
+    const float2 q2 = div(bf16x2_to_f2(v.z));
+    const float2 q3 = div(bf16x2_to_f2(v.w));
     uint2 o;
     if constexpr (INT8) {
-        uint32_t b[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int q = __float2int_rn(div(f[j]));
-            q = max(-127, min(127, q));
-            b[j] = (uint32_t)q & 0xFFu;
-        }
-        o.x = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-        o.y = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
+        auto b = [](float f) { return (uint32_t)max(-127, min(127, __float2int_rn(f))) & 0xFFu; };
+        o.x = b(q0.x) | (b(q0.y) << 8) | (b(q1.x) << 16) | (b(q1.y) << 24);
+        o.y = b(q2.x) | (b(q2.y) << 8) | (b(q3.x) << 16) | (b(q3.y) << 24);
     } else {
-        // sign bits of a bf16 pair (bits 15 and 31) moved to bits 7 and 15 of a code pair
-        auto sgn = [](uint32_t w) { return ((w >> 8) & 0x80u) | ((w >> 16) & 0x8000u); };
-        const uint32_t p0 = cvt_e4m3x2(div(f[0]), div(f[1])) | sgn(v.x);
-        const uint32_t p1 = cvt_e4m3x2(div(f[2]), div(f[3])) | sgn(v.y);
-        const uint32_t p2 = cvt_e4m3x2(div(f[4]), div(f[5])) | sgn(v.z);
-        const uint32_t p3 = cvt_e4m3x2(div(f[6]), div(f[7])) | sgn(v.w);
-        o.x = p0 | (p1 << 16);
-        o.y = p2 | (p3 << 16);
+        // code pairs -> words; sign bytes (byte 1 and 3 of each bf16 pair) gathered with one permute
+        o.x = __byte_perm(cvt_e4m3x2(q0.x, q0.y), cvt_e4m3x2(q1.x, q1.y), 0x5410) | (__byte_perm(v.x, v.y, 0x7531) & 0x80808080u);
+        o.y = __byte_perm(cvt_e4m3x2(q2.x, q2.y), cvt_e4m3x2(q3.x, q3.y), 0x5410) | (__byte_perm(v.z, v.w, 0x7531) & 0x80808080u);
     }
     return o;
 }
 
 // Same for eight fp32 values that are not bf16 images (RMSNorm prologue output).
-__device__ __forceinline__ uint2 encode8_f32(const float (&f)[8], const Divider& div) {
+__device__ __forceinline__ uint2 encode8_f32(const float (&f)[8], const Divider2& div) {
     uint32_t p[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        p[j] = cvt_e4m3x2(div(f[2 * j]), div(f[2 * j + 1])) |
+        const float2 q = div(make_float2(f[2 * j], f[2 * j + 1]));
+        p[j] = cvt_e4m3x2(q.x, q.y) |
                ((__float_as_uint(f[2 * j]) >> 24) & 0x80u) | ((__float_as_uint(f[2 * j + 1]) >> 16) & 0x8000u);
     }
     uint2 o;
@@ -82,8 +74,12 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
         const int c = t + i * TPR;
         v[i] = (live && c < nchunks) ? ld_stream16(xr + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
     }
+    {
+        __nv_bfloat162 pm = amax8_packed(v[0]);
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) am = fmaxf(am, amax8(v[i]));
+        for (int i = 1; i < NCHUNK; ++i) pm = __hmax2(pm, amax8_packed(v[i]));
+        am = hmax_halves(pm);
+    }
     am = warp_max(am);
     if constexpr (TPR > 32) {
         __shared__ float s_am[8];
@@ -95,7 +91,7 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
         for (int w = 1; w < WPR; ++w) am = fmaxf(am, s_am[r_in * WPR + w]);
     }
     const float scale = fmaxf(__fdiv_rn(am, INT8 ? kInt8Max : kFp8Max), kScaleFloor);
-    const Divider div(scale);
+    const Divider2 div(scale);
     if (live && t == 0) scales[row] = scale;
     uint8_t* qr = q + row * ((int64_t)nchunks * 8);
 #pragma unroll
@@ -122,7 +118,7 @@ quant_row_long_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__
 #pragma unroll
     for (int w = 1; w < 8; ++w) am = fmaxf(am, s_am[w]);
     const float scale = fmaxf(__fdiv_rn(am, INT8 ? kInt8Max : kFp8Max), kScaleFloor);
-    const Divider div(scale);
+    const Divider2 div(scale);
     if (threadIdx.x == 0) scales[row] = scale;
     uint8_t* qr = q + row * ((int64_t)nchunks * 8);
     for (int c = threadIdx.x; c < nchunks; c += 256)
@@ -181,30 +177,39 @@ int quant_per_token(const void* x, void* q, float* scales, int64_t M, int64_t D,
 
 // ---- 1x128 -----------------------------------------------------------------------------
 // The [M, D] tensor is a flat sequence of 128-element groups (D % 128 == 0) and the scale
-// array [M, D/128] is the same sequence, so no row structure is needed: 16 consecutive lanes
-// own one group, every thread keeps UNROLL chunks in flight.
-template <int UNROLL>
+// array [M, D/128] is the same sequence, so no row structure is needed.  Four lanes own one
+// group: lane (g, s) holds chunks s, s+4, s+8, s+12 of group g, so that every load instruction
+// of a warp covers eight 64-byte runs (full sectors) and the per-group work (amax shuffles,
+// the divisions that produce scale and reciprocal) is amortised over 32 elements per thread.
+template <int ITER>
 __global__ void __launch_bounds__(256)
 quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                   float* __restrict__ scales, int64_t total_chunks) {
-    const int64_t base = (int64_t)blockIdx.x * (256 * UNROLL) + threadIdx.x;
-    uint4 v[UNROLL];
+                   float* __restrict__ scales, int64_t total_groups) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane & 3;
+    const int64_t g0 = ((int64_t)blockIdx.x * 8 + warp) * (8 * ITER) + (lane >> 2);
+    uint4 v[ITER][4];
 #pragma unroll
-    for (int i = 0; i < UNROLL; ++i) {
-        const int64_t c = base + i * 256;
-        v[i] = (c < total_chunks) ? ld_stream16(x + c * 8) : make_uint4(0, 0, 0, 0);
+    for (int it = 0; it < ITER; ++it) {
+        const int64_t g = g0 + 8 * it;
+        const __nv_bfloat16* src = x + (g * 16 + sub) * 8;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[it][k] = (g < total_groups) ? ld_stream16(src + k * 32) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int i = 0; i < UNROLL; ++i) {
-        const int64_t c = base + i * 256;
-        float am = amax8(v[i]);
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+    for (int it = 0; it < ITER; ++it) {
+        const int64_t g = g0 + 8 * it;
+        float am = hmax_halves(__hmax2(__hmax2(amax8_packed(v[it][0]), amax8_packed(v[it][1])),
+                                       __hmax2(amax8_packed(v[it][2]), amax8_packed(v[it][3]))));
+        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 2));
         const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
-        const Divider div(scale);
-        if (c < total_chunks) {
-            *reinterpret_cast<uint2*>(q + c * 8) = encode8<false>(v[i], div);
-            if ((threadIdx.x & 15) == 0) scales[c >> 4] = scale;
+        const Divider2 div(scale);
+        if (g < total_groups) {
+            uint8_t* dst = q + (g * 16 + sub) * 8;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) *reinterpret_cast<uint2*>(dst + k * 32) = encode8<false>(v[it][k], div);
+            if (sub == 0) scales[g] = scale;
         }
     }
 }
@@ -255,7 +260,7 @@ rmsnorm_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
         const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
-        const Divider div(scale);
+        const Divider2 div(scale);
         if (ok) {
             *reinterpret_cast<uint2*>(q + (row * nchunks + c) * 8) = encode8_f32(f, div);
             if ((t & 15) == 0) scales[(row * nchunks + c) >> 4] = scale;
@@ -288,7 +293,7 @@ quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ 
 #pragma unroll
     for (int k = 1; k < 8; ++k) am = fmaxf(am, s_am[k]);
     const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
-    const Divider div(scale);
+    const Divider2 div(scale);
     if (t == 0) scales[(int64_t)kb * n_tiles + nb] = scale;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -328,11 +333,11 @@ int hkb_quant_fp8_1x128(const void* x, const void* w, void* q, float* scales, in
 #undef HKB_RMS
         return check_launch("rmsnorm_quant_1x128_kernel");
     }
-    constexpr int UNROLL = 4;
-    const int64_t total = M * D / 8;
-    const int64_t grid = (total + 256 * UNROLL - 1) / (256 * UNROLL);
+    constexpr int ITER = 2;
+    const int64_t groups = M * (D / 128);
+    const int64_t grid = (groups + 64 * ITER - 1) / (64 * ITER);
     HKB_REQUIRE(grid <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_fp8_1x128: tensor too large");
-    quant_1x128_kernel<UNROLL><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)q, scales, total);
+    quant_1x128_kernel<ITER><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)q, scales, groups);
     return check_launch("quant_1x128_kernel");
 }
 

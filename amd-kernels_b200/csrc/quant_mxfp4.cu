@@ -2,31 +2,33 @@
 // nibble) with one e8m0 exponent byte per 32 contiguous elements.
 //
 // HBM-bound streaming kernel.  The [M, D] tensor is a flat sequence of 32-element blocks
-// (D % 32 == 0) and the scale array [M, D/32] is the same sequence, so 4 consecutive lanes
-// (8 bf16 each, one 16-byte load) own one block: two shuffles give the block amax, the
-// exponent is read from amax's bit pattern, each lane emits 4 code bytes and every 16th lane
-// emits four scale bytes as one word.
+// (D % 32 == 0) and the scale array [M, D/32] is the same sequence, so two adjacent lanes own
+// one block (two 16-byte chunks each; a lane pair reads a full 32-byte sector per load): one
+// shuffle gives the block amax, the exponent is read from amax's bit pattern, each lane emits
+// 4 code bytes per chunk and every 8th lane emits four scale bytes as one word.
 //
 // Rounding rule of mode 0: nearest E2M1 magnitude of x / 2^e with ties to the SMALLER
 // magnitude, saturating at 6; sign nibble set iff x < 0.  For bf16 inputs x / 2^e carries at
 // most 8 significant bits, so subtracting 2^-12 from |q| turns every tie into a non-tie
 // without moving any other value across a rounding boundary; the hardware round-to-nearest
-// conversion (cvt.rn.satfinite.e2m1x2.f32) then yields exactly that rule.  fp32 inputs (the
-// RMSNorm prologue) and mode 1 (truncation) use explicit threshold compares.
+// conversion (cvt.rn.satfinite.relu.e2m1x2.f32 on |q| - 2^-12; relu turns the slightly negative
+// results of tiny inputs into +0) then yields exactly that rule.  fp32 inputs (the RMSNorm
+// prologue) and mode 1 (truncation) use explicit threshold compares.
 #include "common.cuh"
 
 namespace hkb {
 namespace {
 
 // eight floats -> eight e2m1 nibbles in one word, element j in bits 4j..4j+3
+// (negative inputs give +0: callers pass magnitudes and add the sign bits themselves)
 __device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&r)[8]) {
     uint32_t o;
     asm("{\n"
         ".reg .b8 b0, b1, b2, b3;\n"
-        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
-        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
-        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
-        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "cvt.rn.satfinite.relu.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.relu.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.relu.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.relu.e2m1x2.f32 b3, %8, %7;\n"
         "mov.b32 %0, {b0, b1, b2, b3};\n"
         "}"
         : "=r"(o)
@@ -61,17 +63,21 @@ __device__ __forceinline__ void block_exponent(float amax, uint32_t& scale_byte,
 
 template <int MODE>
 __device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
-    float f[8];
-    unpack8(v, f);
     if constexpr (MODE == HKB_MXFP4_MODE_KERNEL) {
+        float f[8];
+        unpack8(v, f);
         uint32_t o = 0;
 #pragma unroll
         for (int j = 0; j < 8; ++j) o |= nibble_compare(f[j] * inv, MODE) << (4 * j);
         return o;
     } else {
-        float r[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) r[j] = fmaxf(fabsf(f[j] * inv) - 0x1p-12f, 0.0f);
+        // |x| * 2^-e - 2^-12 on the packed fp32 pipe, magnitudes straight from the masked bf16 bits
+        const float2 inv2 = make_float2(inv, inv), nd2 = make_float2(-0x1p-12f, -0x1p-12f);
+        const float2 m0 = __ffma2_rn(bf16x2_to_f2(v.x & 0x7FFF7FFFu), inv2, nd2);
+        const float2 m1 = __ffma2_rn(bf16x2_to_f2(v.y & 0x7FFF7FFFu), inv2, nd2);
+        const float2 m2 = __ffma2_rn(bf16x2_to_f2(v.z & 0x7FFF7FFFu), inv2, nd2);
+        const float2 m3 = __ffma2_rn(bf16x2_to_f2(v.w & 0x7FFF7FFFu), inv2, nd2);
+        const float r[8] = {m0.x, m0.y, m1.x, m1.y, m2.x, m2.y, m3.x, m3.y};
         // sign nibble bit = "x < 0" = sign bit set and magnitude non-zero, from the bf16 bits
         // themselves (a product that underflows to zero must still carry it)
         auto sgn = [](uint32_t w) {
@@ -83,43 +89,48 @@ __device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
     }
 }
 
-// Writes the scale bytes of the 4 blocks a 16-lane group owns.
-__device__ __forceinline__ void store_scales(uint8_t* scales, int64_t c, int64_t total_chunks, uint32_t sb) {
-    const int lane = threadIdx.x & 31;
-    const int g0 = lane & 16;
-    uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, g0) | (__shfl_sync(0xFFFFFFFFu, sb, g0 + 4) << 8) |
-                    (__shfl_sync(0xFFFFFFFFu, sb, g0 + 8) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, g0 + 12) << 24);
-    const int64_t c16 = c & ~(int64_t)15;
-    if (c16 + 16 <= total_chunks) {
-        if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(scales + (c >> 2)) = word;
-    } else if (c < total_chunks && (lane & 3) == 0) {
-        scales[c >> 2] = (uint8_t)sb;
-    }
-}
-
-template <int MODE, int UNROLL>
+// Two adjacent lanes own one 32-element block: lane (b, h) holds chunks 2k + h (k = 0, 1) of
+// block b.  A warp covers 16 blocks per iteration, a thread keeps 2 * ITER chunks in flight.
+template <int MODE, int ITER>
 __global__ void __launch_bounds__(256)
 quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ codes,
-                   uint8_t* __restrict__ scales, int64_t total_chunks) {
-    const int64_t base = (int64_t)blockIdx.x * (256 * UNROLL) + threadIdx.x;
-    uint4 v[UNROLL];
+                   uint8_t* __restrict__ scales, int64_t total_blocks) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = lane & 1;
+    const int64_t b0 = ((int64_t)blockIdx.x * 8 + warp) * (16 * ITER) + (lane >> 1);
+    uint4 v[ITER][2];
 #pragma unroll
-    for (int i = 0; i < UNROLL; ++i) {
-        const int64_t c = base + i * 256;
-        v[i] = (c < total_chunks) ? ld_stream16(x + c * 8) : make_uint4(0, 0, 0, 0);
+    for (int it = 0; it < ITER; ++it) {
+        const int64_t b = b0 + 16 * it;
+        const __nv_bfloat16* src = x + (b * 4 + h) * 8;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) v[it][k] = (b < total_blocks) ? ld_stream16(src + k * 16) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int i = 0; i < UNROLL; ++i) {
-        const int64_t c = base + i * 256;
-        float am = amax8(v[i]);
+    for (int it = 0; it < ITER; ++it) {
+        const int64_t b = b0 + 16 * it;
+        float am = hmax_halves(__hmax2(amax8_packed(v[it][0]), amax8_packed(v[it][1])));
         am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
-        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 2));
         uint32_t sb;
         float inv;
         block_exponent<MODE>(am, sb, inv);
-        const uint32_t out = encode8_bf16<MODE>(v[i], inv);
-        if (c < total_chunks) *reinterpret_cast<uint32_t*>(codes + c * 4) = out;
-        store_scales(scales, c, total_chunks, sb);
+        const uint32_t c0 = encode8_bf16<MODE>(v[it][0], inv);
+        const uint32_t c1 = encode8_bf16<MODE>(v[it][1], inv);
+        if (b < total_blocks) {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(codes + (b * 4 + h) * 4);
+            dst[0] = c0;
+            dst[2] = c1;
+        }
+        // scale bytes of 4 consecutive blocks (lanes 8j, 8j+2, 8j+4, 8j+6) go out as one word
+        const int l8 = lane & 24;
+        const uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, l8) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 2) << 8) |
+                              (__shfl_sync(0xFFFFFFFFu, sb, l8 + 4) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 6) << 24);
+        const int64_t b4 = b & ~(int64_t)3;
+        if (b4 + 4 <= total_blocks) {
+            if ((lane & 7) == 0) *reinterpret_cast<uint32_t*>(scales + b) = word;
+        } else if (b < total_blocks && h == 0) {
+            scales[b] = (uint8_t)sb;
+        }
     }
 }
 
@@ -206,13 +217,13 @@ extern "C" int hkb_quant_mxfp4(const void* x, const void* w, void* codes, void* 
 #undef HKB_RMS
         return check_launch("rmsnorm_quant_mxfp4_kernel");
     }
-    constexpr int UNROLL = 4;
-    const int64_t total = M * D / 8;
-    const int64_t grid = (total + 256 * UNROLL - 1) / (256 * UNROLL);
+    constexpr int ITER = 4;
+    const int64_t blocks = M * (D / 32);
+    const int64_t grid = (blocks + 128 * ITER - 1) / (128 * ITER);
     HKB_REQUIRE(grid <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_mxfp4: tensor too large");
     if (mode == HKB_MXFP4_MODE_KERNEL)
-        quant_mxfp4_kernel<HKB_MXFP4_MODE_KERNEL, UNROLL><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, total);
+        quant_mxfp4_kernel<HKB_MXFP4_MODE_KERNEL, ITER><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, blocks);
     else
-        quant_mxfp4_kernel<HKB_MXFP4_MODE_DOC, UNROLL><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, total);
+        quant_mxfp4_kernel<HKB_MXFP4_MODE_DOC, ITER><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, blocks);
     return check_launch("quant_mxfp4_kernel");
 }

@@ -417,7 +417,11 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for ncu: no CPU baseline, no end-to-end loop, no clock sampling")
     args = ap.parse_args()
+    if args.profile:
+        args.no_cpu_baseline = args.no_e2e = True
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -442,7 +446,7 @@ def main():
 
     peaks = load_peaks()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not args.profile:
         sampler.start()          # nvidia-smi needs a moment to start; samples are cut to the timed part below
     wl = Workload(name, rank, world, dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
@@ -492,7 +496,7 @@ def main():
     # nvidia-smi samples every 100 ms; a short timed region would be missed, so the same step keeps
     # running (untimed) until 1.5 s of load have been sampled.  Samples start with the timed steps.
     t_load = time.time()
-    while time.time() - t_load < max(0.0, 1.5 - (ms + dom_ms * args.steps) / 1e3):
+    while not args.profile and time.time() - t_load < max(0.0, 1.5 - (ms + dom_ms * args.steps) / 1e3):
         for _ in range(20):
             wl.step()
         torch.cuda.synchronize()
