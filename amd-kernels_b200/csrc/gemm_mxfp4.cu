@@ -14,6 +14,8 @@
 // Roles, ring, bounded waits and teardown are those of the FP8 kernel (gemm_fp8.cu).
 #include "tc_common.cuh"
 
+#include <mutex>
+
 namespace hkb {
 namespace {
 
@@ -35,8 +37,9 @@ struct Mxfp4Params {
 };
 
 // Row-major e8m0 [batch, R, K/32] -> atoms [batch, ceil(R/128), katoms_pad, 512 B]; rows past R
-// and atoms past K/128 are written as zero bytes (they meet zero-filled operand data).  One CTA moves 128 rows x 32 atoms through shared memory so that both
-// the global reads (128 B per row) and writes (512 B per atom) are coalesced.
+// and atoms past K/128 are written as zero bytes (they meet zero-filled operand data).  One CTA
+// moves 128 rows x 32 atoms through shared memory so that both the global reads (128 B per row)
+// and writes (512 B per atom) are coalesced.
 __global__ void __launch_bounds__(256)
 sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int R, int katoms, int katoms_pad, int rblks) {
     __shared__ uint32_t tile[32][129];   // [atom in chunk][word in atom], padded
@@ -288,6 +291,120 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
     if (rc != HKB_OK) return rc;
     const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
     HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    const int tiles = p.m_blks * p.n_blks * p.batch;
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
+    gemm_mxfp4_kernel<<<tiles < sms ? tiles : sms, 192, Smem::kDynamic, st>>>(tmA, tmB, p);
+    return check_launch("gemm_mxfp4_kernel");
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers must not trigger a device allocation at call time: code that runs inside a
+// memory-pool or arena discipline where every byte is accounted for up front, latency-critical
+// serving loops where cudaMalloc's implicit device synchronisation is unacceptable, and hosts
+// that hand this library a device on which they have already claimed all memory.  For them the
+// re-laid-out scale factors live in a fixed array that is part of the library image: every GPU
+// that loads libhkb200.so reserves it until the process exits.
+//
+//   * Limit: the scales of both operands, padded to 128-row blocks and an even number of
+//     128-wide K atoms, must fit kStaticSfBytes (8 MiB); e.g. M + N <= 32768 rows at K = 8192.
+//     Larger problems are refused with HKB_ERR_BAD_SHAPE; nothing is launched.
+//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+//     that device current) and sets the kernel's shared-memory attribute.  Make that first call
+//     outside any stream capture.
+//   * Every call on a device shares the one array, which keeps the previous call's contents.
+//     Nothing in it has to start at zero: the re-layout pass rewrites every byte the GEMM reads,
+//     including the zero padding of partial row blocks and of an odd K atom.  Two calls that can
+//     overlap on the GPU (different streams, or different host threads) race on the array; run
+//     them in one stream or order them with events.
+//   * Bounded-wait timeouts of this variant are recorded in a word of the same image
+//     (g_static_status), not in the word hkb_check_status() reads.
+namespace hkb {
+namespace {
+
+constexpr size_t kStaticSfBytes = (size_t)8 << 20;
+static __device__ __align__(256) uint8_t g_static_sf[kStaticSfBytes];
+static __device__ __align__(256) uint32_t g_static_status[64];
+
+struct StaticSlot {
+    uint8_t* sf = nullptr;       // device address of g_static_sf on this device
+    uint32_t* status = nullptr;  // device address of g_static_status on this device
+};
+StaticSlot g_static_slot[64];
+std::mutex g_static_mu;
+
+// Device addresses of the static arrays for the CURRENT device (looked up once per device).
+int static_addresses(StaticSlot* out) {
+    int dev = 0;
+    HKB_CUDA(cudaGetDevice(&dev));
+    HKB_REQUIRE(dev >= 0 && dev < 64, HKB_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    StaticSlot& s = g_static_slot[dev];
+    if (!s.sf) {
+        void* p = nullptr;
+        void* q = nullptr;
+        // In host code the array names are host-side handles, not device addresses: ask the runtime.
+        HKB_CUDA(cudaGetSymbolAddress(&p, g_static_sf));
+        HKB_CUDA(cudaGetSymbolAddress(&q, g_static_status));
+        HKB_CUDA(cudaFuncSetAttribute(gemm_mxfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic));
+        s.status = static_cast<uint32_t*>(q);
+        s.sf = static_cast<uint8_t*>(p);
+    }
+    *out = s;
+    return HKB_OK;
+}
+
+}  // namespace
+}  // namespace hkb
+
+extern "C" int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                                     int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(A && B && C && sfa && sfb, HKB_ERR_BAD_ARG, "gemm_mxfp4_static: null pointer");
+    HKB_REQUIRE(batch >= 1 && M >= 1 && N >= 1 && K >= 1, HKB_ERR_BAD_SHAPE, "gemm_mxfp4_static: empty problem");
+    HKB_REQUIRE(K % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4_static: K=%lld must be a multiple of 128", (long long)K);
+    HKB_REQUIRE(N % 8 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4_static: N=%lld must be a multiple of 8", (long long)N);
+    HKB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) && batch < 65536, HKB_ERR_BAD_SHAPE,
+                "gemm_mxfp4_static: dimension too large");
+    HKB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && ((uintptr_t)sfa & 3) == 0 && ((uintptr_t)sfb & 3) == 0,
+                HKB_ERR_BAD_ALIGN, "gemm_mxfp4_static: A, B, C must be 16-byte and the scale arrays 4-byte aligned");
+    Mxfp4Params p{};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.m_blks = (int)((M + BM - 1) / BM);
+    p.n_blks = (int)((N + BN - 1) / BN);
+    const int katoms_src = (int)(K / 128);
+    p.katoms = (katoms_src + 1) & ~1;
+    p.C = (__nv_bfloat16*)C;
+    const size_t sfa_bytes = (size_t)batch * p.m_blks * p.katoms * 512;
+    const size_t sfb_bytes = (size_t)batch * p.n_blks * p.katoms * 512;
+    HKB_REQUIRE(sfa_bytes + sfb_bytes <= kStaticSfBytes, HKB_ERR_BAD_SHAPE,
+                "gemm_mxfp4_static: the scale factors need %zu bytes of scratch but the built-in array holds %zu "
+                "(limit: batch * (ceil(M/128) + ceil(N/128)) * ceil(K/256) * 1024 <= 8 MiB); use hkb_gemm_mxfp4",
+                sfa_bytes + sfb_bytes, kStaticSfBytes);
+    HKB_REQUIRE(p.m_blks <= 65535 && p.n_blks <= 65535, HKB_ERR_BAD_SHAPE, "gemm_mxfp4_static: too many row blocks");
+    StaticSlot slot;
+    int rc = static_addresses(&slot);
+    if (rc != HKB_OK) return rc;
+    p.status = slot.status;
+    uint8_t* sfa_sw = slot.sf;
+    uint8_t* sfb_sw = slot.sf + sfa_bytes;          // sfa_bytes is a multiple of 1024
+    p.sfa = sfa_sw;
+    p.sfb = sfb_sw;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)p.m_blks, (unsigned)batch);
+    sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)sfa, sfa_sw, (int)M, katoms_src, p.katoms, p.m_blks);
+    dim3 gb((unsigned)((p.katoms + 31) / 32), (unsigned)p.n_blks, (unsigned)batch);
+    sf_relayout_kernel<<<gb, 256, 0, st>>>((const uint8_t*)sfb, sfb_sw, (int)N, katoms_src, p.katoms, p.n_blks);
+    rc = check_launch("sf_relayout_kernel");
+    if (rc != HKB_OK) return rc;
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)batch, BM);
+    if (rc != HKB_OK) return rc;
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, BN);
+    if (rc != HKB_OK) return rc;
     const int tiles = p.m_blks * p.n_blks * p.batch;
     const int sms = sm_count();
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");

@@ -107,6 +107,20 @@ int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* 
 int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                    int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* hkb_gemm_mxfp4 for callers that must not allocate device memory at call time (arena / pool
+ * disciplines that account for every byte up front, serving loops that cannot take cudaMalloc's
+ * device-wide synchronisation, devices whose memory the host has already claimed in full).
+ * Same arguments and results as hkb_gemm_mxfp4; the re-laid-out scale factors go into an 8 MiB
+ * array built into the library image instead of grown scratch, so it calls no cudaMalloc/cudaFree.
+ * Limit: batch * (ceil(M/128) + ceil(N/128)) * ceil(K/256) * 1024 bytes <= 8 MiB (e.g. M + N <=
+ * 32768 at K = 8192); beyond it HKB_ERR_BAD_SHAPE is returned and nothing is launched.  The first
+ * call on each device resolves the array's device address: make it outside stream capture.  All
+ * calls on a device share the array; calls that may overlap on the GPU race on it and must be
+ * ordered by the caller.  Bounded-wait failures of this variant are not visible to hkb_check_status.
+ * No counterpart in the reference project. */
+int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                          int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,76 @@
+"""GPU tier, collected last: the allocation-free MXFP4 GEMM entry point.
+
+`hkb_gemm_mxfp4_static` serves callers that cannot let a library allocate device memory while
+they run (fixed memory arenas, latency-critical loops, fully claimed devices): its scale-factor
+scratch is an array inside the library image.  It must give the same output as `hkb_gemm_mxfp4`
+through the C ABI, on consecutive calls that reuse the shared array with different shapes, and
+must refuse problems whose scales do not fit the array.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemm as ogemm, quant as oquant
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+i64 = ctypes.c_int64
+TOL = 1e-2      # same bar as the other GEMM parity tests
+
+
+def _lib():
+    lib = ctypes.CDLL(os.path.join(ROOT, "amd-kernels_b200", "kernels", "libhkb200.so"))
+    lib.hkb_last_error.restype = ctypes.c_char_p
+    return lib
+
+
+def _case(M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(M, K, generator=g).bfloat16()
+    W = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    ac, asc = oquant.quant_mxfp4(A)
+    wc, wsc = oquant.quant_mxfp4(W)
+    return [torch.from_numpy(t).cuda() for t in (ac, wc, asc, wsc)], (ac, wc, asc, wsc)
+
+
+def _call(fn, t, M, N, K):
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = [ctypes.c_void_p(x.data_ptr()) for x in t]
+    rc = fn(p[0], p[1], ctypes.c_void_p(C.data_ptr()), p[2], p[3], i64(1), i64(M), i64(N), i64(K), stream)
+    torch.cuda.synchronize()
+    return rc, C
+
+
+def test_static_scratch_entry_point_matches_the_allocating_one_on_two_calls_in_a_row():
+    lib = _lib()
+    torch.cuda.set_device(0)
+    # second call is smaller and has an odd number of K atoms: it must not see the first call's scales
+    for (M, N, K, seed) in [(256, 384, 512, 11), (200, 136, 384, 12)]:
+        t, host = _case(M, N, K, seed)
+        rc_ref, C_ref = _call(lib.hkb_gemm_mxfp4, t, M, N, K)
+        rc_new, C_new = _call(lib.hkb_gemm_mxfp4_static, t, M, N, K)
+        assert rc_ref == 0, lib.hkb_last_error().decode()
+        assert rc_new == 0, lib.hkb_last_error().decode()
+        assert not torch.isnan(C_new.float()).any()
+        err = ogemm.rel_err(C_new.float().cpu().numpy(), C_ref.float().cpu().numpy())
+        assert err <= TOL, f"static vs allocating entry point: rel_err {err} at {(M, N, K)}"
+        oracle = ogemm.gemm_mxfp4(*host)
+        assert ogemm.rel_err(C_new.float().cpu().numpy(), oracle) <= TOL
+
+
+def test_static_scratch_entry_point_refuses_what_does_not_fit():
+    lib = _lib()
+    t, _ = _case(128, 128, 128, 13)
+    p = [ctypes.c_void_p(x.data_ptr()) for x in t]
+    C = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
+    # pointers are valid but the declared problem needs 16 MiB of scale scratch: refused up front
+    rc = lib.hkb_gemm_mxfp4_static(p[0], p[1], ctypes.c_void_p(C.data_ptr()), p[2], p[3],
+                                   i64(1), i64(32768), i64(32768), i64(8192), None)
+    assert rc == -2
+    assert b"8 MiB" in lib.hkb_last_error()
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(C).item() == 0
