@@ -83,6 +83,18 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return v;
 }
 
+// 16 bf16 = 32 bytes moved by one 256-bit load (sm_100+), as two 16-byte halves.
+struct Wide { uint4 lo, hi; };
+__device__ __forceinline__ Wide ld_stream32(const void* p) {
+    Wide v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ Wide wide_zero() { Wide v; v.lo = make_uint4(0, 0, 0, 0); v.hi = v.lo; return v; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
+
 // Two floats -> two e4m3fn bytes (round-to-nearest-even, saturating to +-448), `lo` in bits 0-7.
 __device__ __forceinline__ uint16_t cvt_e4m3x2(float lo, float hi) {
     uint16_t r;
@@ -146,6 +158,7 @@ __device__ __forceinline__ __nv_bfloat162 amax8_packed(const uint4& v) {
     return __hmax2(__hmax2(*reinterpret_cast<__nv_bfloat162*>(&x0), *reinterpret_cast<__nv_bfloat162*>(&x1)),
                    __hmax2(*reinterpret_cast<__nv_bfloat162*>(&x2), *reinterpret_cast<__nv_bfloat162*>(&x3)));
 }
+__device__ __forceinline__ __nv_bfloat162 amax16_packed(const Wide& v) { return __hmax2(amax8_packed(v.lo), amax8_packed(v.hi)); }
 __device__ __forceinline__ float hmax_halves(__nv_bfloat162 m) { return fmaxf(__low2float(m), __high2float(m)); }
 
 __device__ __forceinline__ float warp_max(float v) {

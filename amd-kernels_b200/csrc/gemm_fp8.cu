@@ -23,6 +23,7 @@
 // the device status word (read by hkb_check_status), stops issuing work, and still frees TMEM.
 #include "tc_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace hkb {
@@ -78,10 +79,13 @@ struct GemmParams {
     uint32_t* status;
 };
 
-template <int BN, int STAGES>
+// kPair: two CTAs (a cluster of 2) share one 256 x BN tile; each stages its own 128 rows of A
+// and its own half of B's BN rows.
+template <int BN, int STAGES, bool kPair = false>
 struct SmemLayout {
     static constexpr int kABytes = BM * BK;
-    static constexpr int kBBytes = BN * BK;
+    static constexpr int kBRows = kPair ? BN / 2 : BN;
+    static constexpr int kBBytes = kBRows * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = STAGES * kStageBytes;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
@@ -103,30 +107,50 @@ __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* dst, const float* v)
     *reinterpret_cast<uint4*>(dst) = o;
 }
 
-// Writes 32 consecutive columns of one output row (N % 8 == 0 keeps 16-byte stores aligned).
-__device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N, const float* v) {
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+// 16 bf16 (32 bytes) with one 256-bit store: a warp whose lanes write different rows pays one
+// L1 wavefront per row and per instruction, so wider stores halve that cost.
+__device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const float* v) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(dst), "r"(pack_bf16(v[0], v[1])), "r"(pack_bf16(v[2], v[3])), "r"(pack_bf16(v[4], v[5])),
+                   "r"(pack_bf16(v[6], v[7])), "r"(pack_bf16(v[8], v[9])), "r"(pack_bf16(v[10], v[11])),
+                   "r"(pack_bf16(v[12], v[13])), "r"(pack_bf16(v[14], v[15])) : "memory");
+}
+// Writes 32 consecutive columns of one output row.  `wide` = rows are 32-byte aligned (N % 16 == 0);
+// otherwise 16-byte stores (N % 8 == 0 is guaranteed).
+__device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N, const float* v, bool wide) {
+    if (wide) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 8)
-        if (col0 + j < N) store_bf16x8(crow + col0 + j, v + j);
+        for (int j = 0; j < 32; j += 16)
+            if (col0 + j < N) store_bf16x16(crow + col0 + j, v + j);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8)
+            if (col0 + j < N) store_bf16x8(crow + col0 + j, v + j);
+    }
 }
 
-template <int BN, bool kBlockScale>
-constexpr int gemm_threads() { return (kBlockScale ? 128 : 64) + 128 * (BN == 256 ? 2 : 1); }
+template <int BN, bool kBlockScale, bool kPair = false>
+constexpr int gemm_threads() { return ((kBlockScale || kPair) ? 128 : 64) + 128 * (BN == 256 ? 2 : 1); }
 
 __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, float2 c) {
     return __ffma2_rn(make_float2(__uint_as_float(a0), __uint_as_float(a1)), s, c);
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128>
-__global__ void __launch_bounds__(gemm_threads<BN, kBlockScale>(), 1)
+template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false>
+__global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, kPair>;
+    static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
     constexpr int EPI_WARPS = 4 * EPI_GROUPS;
     constexpr int COLS_PER_GROUP = BN / EPI_GROUPS;
     constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
-    constexpr uint32_t IDESC = idesc_f8(BM, BN);
-    constexpr int EPI_WARP0 = kBlockScale ? 4 : 2;      // first epilogue warp
+    constexpr uint32_t IDESC = idesc_f8(kPair ? 2 * BM : BM, BN);
+    constexpr int EPI_WARP0 = (kBlockScale || kPair) ? 4 : 2;      // first epilogue warp
     constexpr bool kRegSplit = kBlockScale && BN == 256; // 3 warpgroups: trade registers between them
 
     extern __shared__ uint8_t smem_raw[];
@@ -143,8 +167,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int kblocks = p.K / BK;
+    // pair mode: p.m_blks counts 256-row blocks, a "tile" belongs to the cluster, CTA `rank` owns
+    // rows [rank*128, rank*128+128) of it and stages rows [rank*128, ..) of the tile's B block
+    const uint32_t rank = kPair ? cluster_ctarank() : 0u;
     const int tiles_per_batch = p.m_blks * p.n_blks;
     const int total_tiles = tiles_per_batch * p.batch;
+    const int tile0 = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    constexpr int TILE_M = kPair ? 2 * BM : BM;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -153,14 +183,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), EPI_WARPS);
+            mbar_init(tempty_bar(a), kPair ? 2 * EPI_WARPS : EPI_WARPS);   // the leader hears both CTAs' epilogues
         }
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    if (warp == 1) {
+        if constexpr (kPair) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        else tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) { __syncwarp(); cluster_sync_all(); }   // the partner's barriers and TMEM exist before anyone signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -171,33 +205,40 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (elect_one()) {
             prefetch_tmap(&tmA);
             prefetch_tmap(&tmB);
-            const uint32_t stage_tx = (uint32_t)p.a_box_rows * BK + (uint32_t)L::kBBytes;
+            // pair mode: the leader's full barrier counts the bytes of both CTAs' loads
+            const uint32_t stage_tx = ((uint32_t)p.a_box_rows * BK + (uint32_t)L::kBBytes) * (kPair ? 2u : 1u);
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int t = tile0; t < total_tiles && ok; t += tile_step) {
                 const int b = t / tiles_per_batch;
                 int mb, nb;
-                tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+                tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, mb, nb);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
                     const uint32_t sa = smem_base + s * L::kStageBytes;
-                    tma_load_3d(sa, &tmA, full_bar(s), kb * BK, mb * BM, b);
-                    tma_load_3d(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN, b);
+                    if constexpr (kPair) {
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                        tma_load_3d_pair(sa, &tmA, full_bar(s), kb * BK, mb * TILE_M + (int)rank * BM, b);
+                        tma_load_3d_pair(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN + (int)rank * L::kBRows, b);
+                    } else {
+                        mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                        tma_load_3d(sa, &tmA, full_bar(s), kb * BK, mb * BM, b);
+                        tma_load_3d(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN, b);
+                    }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ================= MMA issuer =================
-        if (elect_one()) {
+        // ================= MMA issuer (pair mode: the leader CTA only) =================
+        if ((!kPair || rank == 0) && elect_one()) {
             int s = 0;
             uint32_t ph = 0;
             int acc = 0;
             uint32_t acc_ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int t = tile0; t < total_tiles && ok; t += tile_step) {
                 if (!kBlockScale) {
                     if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
                     tc_fence_after();
@@ -217,17 +258,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint32_t accumulate = kBlockScale ? (k != 0) : ((kb | k) != 0);
                         // advancing K by 32 bytes inside the 128-byte swizzle row = +2 in the address field
-                        mma_f8(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), IDESC, accumulate);
+                        if constexpr (kPair) mma_f8_pair(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), IDESC, accumulate);
+                        else mma_f8(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), IDESC, accumulate);
                     }
-                    tc_commit(empty_bar(s));           // smem stage free once these MMAs retire
+                    // smem stage free once these MMAs retire (pair mode: in both CTAs)
+                    if constexpr (kPair) tc_commit_pair(empty_bar(s), 3); else tc_commit(empty_bar(s));
                     if (kBlockScale) {
-                        tc_commit(tfull_bar(acc));      // partial product ready for promotion
+                        // partial product ready for promotion
+                        if constexpr (kPair) tc_commit_pair(tfull_bar(acc), 3); else tc_commit(tfull_bar(acc));
                         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!kBlockScale && ok) {
-                    tc_commit(tfull_bar(acc));
+                    if constexpr (kPair) tc_commit_pair(tfull_bar(acc), 3); else tc_commit(tfull_bar(acc));
                     if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                 }
             }
@@ -244,11 +288,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const bool wide = (p.N % 16) == 0;
+        for (int t = tile0; t < total_tiles && ok; t += tile_step) {
             const int b = t / tiles_per_batch;
             int mb, nb;
-            tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
-            const int row = mb * BM + row_in_tile;
+            tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, mb, nb);
+            const int row = mb * TILE_M + (int)rank * BM + row_in_tile;
             const bool row_ok = row < p.M;
             const int col_base = nb * BN + grp * COLS_PER_GROUP;
             __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
@@ -268,18 +313,24 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const int col0 = col_base + c;
                     float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = col0 + j;
-                        const float sbv = col < p.N ? __ldg(sbp + col) : 0.0f;
-                        float x = __uint_as_float(r[j]) * sa * sbv;
-                        if (biasp && col < p.N) x += __bfloat162float(biasp[col]);
-                        v[j] = x;
+                    for (int j = 0; j < 32; j += 8) {          // N % 8 == 0: a group of 8 columns is all in or all out
+                        const bool in = col0 + j < p.N;
+                        const float4 s0 = in ? __ldg(reinterpret_cast<const float4*>(sbp + col0 + j)) : make_float4(0, 0, 0, 0);
+                        const float4 s1 = in ? __ldg(reinterpret_cast<const float4*>(sbp + col0 + j + 4)) : make_float4(0, 0, 0, 0);
+                        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                        float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                        if (biasp && in) {
+                            const uint4 bw = __ldg(reinterpret_cast<const uint4*>(biasp + col0 + j));
+                            unpack8(bw, bv);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[j + i] = __uint_as_float(r[j + i]) * sa * sv[i] + bv[i];
                     }
-                    if (row_ok) store_row32(crow, col0, p.N, v);
+                    if (row_ok) store_row32(crow, col0, p.N, v, wide);
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                if (lane == 0) { if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0); else mbar_arrive(tempty_bar(acc)); }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             } else if constexpr (kGn128) {
                 // one scale per (row, K block) and per (K block, 128 columns): a single fp32 factor
@@ -292,14 +343,26 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const float* sarow = p.sa + (int64_t)(row_ok ? row : p.M - 1) * kbs;
                 const int nsb = p.N / 128;
                 const float* sbcol = p.sb + min(col_base / 128, nsb - 1);
-                float sa_next = __ldg(sarow), sb_next = __ldg(sbcol);
+                // activation scales of this row, four K blocks per (row-strided, hence costly) load
+                const bool sa_vec = (kbs % 4) == 0;
+                auto load_sa4 = [&](int kb4) {
+                    if (kb4 >= kbs) return make_float4(0, 0, 0, 0);
+                    if (sa_vec) return __ldg(reinterpret_cast<const float4*>(sarow + kb4));
+                    float4 q = make_float4(__ldg(sarow + kb4), 0, 0, 0);
+                    if (kb4 + 1 < kbs) q.y = __ldg(sarow + kb4 + 1);
+                    if (kb4 + 2 < kbs) q.z = __ldg(sarow + kb4 + 2);
+                    if (kb4 + 3 < kbs) q.w = __ldg(sarow + kb4 + 3);
+                    return q;
+                };
+                float4 sa_cur = load_sa4(0), sa_nxt = load_sa4(4);
+                float sb_next = __ldg(sbcol);
                 for (int kb = 0; kb < kbs; ++kb) {
-                    const float sc = sa_next * sb_next;
+                    const int sub = kb & 3;
+                    const float sa_k = sub == 0 ? sa_cur.x : sub == 1 ? sa_cur.y : sub == 2 ? sa_cur.z : sa_cur.w;
+                    const float sc = sa_k * sb_next;
                     const float2 s2 = make_float2(sc, sc);
-                    if (kb + 1 < kbs) {                       // next block's scales arrive under this block's work
-                        sa_next = __ldg(sarow + kb + 1);
-                        sb_next = __ldg(sbcol + (int64_t)(kb + 1) * nsb);
-                    }
+                    if (kb + 1 < kbs) sb_next = __ldg(sbcol + (int64_t)(kb + 1) * nsb);   // uniform address: one wavefront
+                    if (sub == 3) { sa_cur = sa_nxt; sa_nxt = load_sa4(kb + 5); }
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
@@ -321,19 +384,19 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     // the partial product now lives in registers: hand the TMEM buffer back before the last FMAs
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                    if (lane == 0) { if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0); else mbar_arrive(tempty_bar(acc)); }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc2[48 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[48 + j]);
                     if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                 }
                 if (ok && row_ok) {
+                    // N % 128 == 0 in block-scale mode: rows are 32-byte aligned, whole groups are in range
 #pragma unroll
-                    for (int c = 0; c < 128; c += 8) {
-                        if (col_base + c < p.N) {
-                            const float v[8] = {acc2[c / 2].x, acc2[c / 2].y, acc2[c / 2 + 1].x, acc2[c / 2 + 1].y,
-                                                acc2[c / 2 + 2].x, acc2[c / 2 + 2].y, acc2[c / 2 + 3].x, acc2[c / 2 + 3].y};
-                            store_bf16x8(crow + col_base + c, v);
-                        }
+                    for (int c = 0; c < 128; c += 16) {
+                        float v[16];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { v[2 * i] = acc2[c / 2 + i].x; v[2 * i + 1] = acc2[c / 2 + i].y; }
+                        store_bf16x16(crow + col_base + c, v);
                     }
                 }
             } else {
@@ -365,12 +428,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                    if (lane == 0) { if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0); else mbar_arrive(tempty_bar(acc)); }
                     if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                 }
                 if (ok && row_ok) {
 #pragma unroll
-                    for (int c = 0; c < COLS_PER_GROUP; c += 32) store_row32(crow, col_base + c, p.N, accv + c);
+                    for (int c = 0; c < COLS_PER_GROUP; c += 32) store_row32(crow, col_base + c, p.N, accv + c, wide);
                 }
             }
         }
@@ -379,6 +442,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ---- teardown: every role is done (or has given up); free TMEM ----
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) { __syncwarp(); cluster_sync_all(); }   // the partner is done with this CTA's smem, barriers and TMEM
     if (warp == 1) {
         if (*abort_flag) {
             // give copies that may still be in flight time to land before the CTA exits
@@ -386,8 +450,43 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if constexpr (kPair) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
     }
+}
+
+// CTA-pair launch: clusters of 2 along x, one cluster per pair of SMs, persistent over 256 x 256 tiles.
+template <int STAGES, bool kBlockScale>
+int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
+    using L = SmemLayout<256, STAGES, true>;
+    auto kern = gemm_fp8_kernel<256, STAGES, kBlockScale, true, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(e));
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 1, HKB_ERR_CUDA, "no CUDA device");
+    const int tiles = p.m_blks * p.n_blks * p.batch;
+    int clusters = sms / 2;
+    if (tiles < clusters) clusters = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters);
+    cfg.blockDim = dim3(gemm_threads<256, kBlockScale, true>());
+    cfg.dynamicSmemBytes = L::kDynamic;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
+    HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cluster launch of gemm_fp8_kernel failed: %s", cudaGetErrorString(e));
+    return check_launch("gemm_fp8_kernel (CTA pairs)");
+}
+
+// HKB_GEMM_PAIRS=0 in the environment forces the single-CTA kernels (for A/B measurements).
+inline bool pairs_enabled() {
+    static const bool on = [] { const char* v = getenv("HKB_GEMM_PAIRS"); return !(v && v[0] == '0'); }();
+    return on;
 }
 
 template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false>
@@ -444,12 +543,20 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
     if ((int64_t)p.m_blks * ((N + 255) / 256) * batch < 2LL * sms) bn = 128;
     if ((int64_t)p.m_blks * ((N + 127) / 128) * batch < 2LL * sms) bn = 64;
     p.n_blks = (int)((N + bn - 1) / bn);
+    cudaStream_t st = (cudaStream_t)stream;
     CUtensorMap tmA, tmB;
     rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, (uint32_t)p.a_box_rows);
     if (rc != HKB_OK) return rc;
+    // Large problems: CTA pairs on 256 x 256 tiles (a third less operand traffic per SM).
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256) * batch;
+    if (bn == 256 && M > 128 && pair_tiles >= sms / 2 && pairs_enabled()) {
+        p.m_blks = (int)((M + 255) / 256);
+        rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)batch, 128);
+        if (rc != HKB_OK) return rc;
+        return launch_gemm_pair<7, false>(tmA, tmB, p, st);
+    }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)batch, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
     if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, p, st);
     if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, p, st);
     return launch_gemm<64, 8, false>(tmA, tmB, p, st);
@@ -474,12 +581,22 @@ int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* 
     int bn = 256;
     if (gn != 128 || N % 256 != 0 || (int64_t)p.m_blks * (N / 256) < 2LL * sms) bn = 128;
     p.n_blks = (int)(N / bn);
+    cudaStream_t st = (cudaStream_t)stream;
     CUtensorMap tmA, tmB;
     rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)M, 1, BM);
     if (rc != HKB_OK) return rc;
+    // CTA pairs do not pay off here: the per-K-block accumulator hand-off would cross the cluster
+    // (measured ~2x slower than the single-CTA kernel); kept reachable for experiments only.
+    static const bool bs_pairs = [] { const char* v = getenv("HKB_BLOCKSCALE_PAIRS"); return v && v[0] == '1'; }();
+    const int64_t pair_tiles = ((M + 255) / 256) * (N / 256);
+    if (bs_pairs && bn == 256 && M > 128 && pair_tiles >= sms / 2) {
+        p.m_blks = (int)((M + 255) / 256);
+        rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, 128);
+        if (rc != HKB_OK) return rc;
+        return launch_gemm_pair<7, true>(tmA, tmB, p, st);
+    }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
     if (gn == 128) {
         if (bn == 256) return launch_gemm<256, 4, true, true>(tmA, tmB, p, st);
         return launch_gemm<128, 6, true, true>(tmA, tmB, p, st);

@@ -1,9 +1,9 @@
 // FP8 (e4m3fn) dynamic quantizers for sm_100a: per-row, 1x128 block and 128x128 block scales.
 //
-// All three are HBM-bound streaming kernels: every thread moves 16-byte chunks (8 bf16) with
-// coalesced no-allocate loads, keeps them in registers between the amax pass and the convert
+// All three are HBM-bound streaming kernels: every thread moves 32-byte chunks (16 bf16, one
+// 256-bit no-allocate load), keeps them in registers between the amax pass and the convert
 // pass (the input is read from HBM exactly once), reduces |x| maxima with warp shuffles and
-// writes packed e4m3 bytes with 8-byte stores.  Arithmetic is IEEE fp32 and reproduces
+// writes packed e4m3 bytes with 16-byte stores.  Arithmetic is IEEE fp32 and reproduces
 //   scale = max(amax / 448, 1e-10);  q = e4m3fn_rne(clamp(x / scale, +-448))
 // bit for bit (see hkb::Divider for the exactly rounded shared-divisor division).
 #include "common.cuh"
@@ -37,6 +37,12 @@ __device__ __forceinline__ uint2 encode8(const uint4& v, const Divider2& div) {
     return o;
 }
 
+template <bool INT8>
+__device__ __forceinline__ uint4 encode16(const Wide& v, const Divider2& div) {
+    const uint2 a = encode8<INT8>(v.lo, div), b = encode8<INT8>(v.hi, div);
+    return make_uint4(a.x, a.y, b.x, b.y);
+}
+
 // Same for eight fp32 values that are not bf16 images (RMSNorm prologue output).
 __device__ __forceinline__ uint2 encode8_f32(const float (&f)[8], const Divider2& div) {
     uint32_t p[4];
@@ -53,12 +59,12 @@ __device__ __forceinline__ uint2 encode8_f32(const float (&f)[8], const Divider2
 }
 
 // ---- per-row ---------------------------------------------------------------------------
-// A CTA of 256 threads covers 256/TPR rows; TPR threads share a row and each holds NCHUNK
-// chunks (chunk index = t + i*TPR) in registers.
-template <int NCHUNK, int TPR, bool INT8>
+// A CTA of 256 threads covers 256/TPR rows; TPR threads share a row and each holds NW 32-byte
+// chunks (chunk index = t + i*TPR) in registers.  Needs D % 16 == 0 and 32-byte aligned rows.
+template <int NW, int TPR, bool INT8>
 __global__ void __launch_bounds__(256)
 quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                 float* __restrict__ scales, int64_t M, int nchunks, int64_t ldx) {
+                 float* __restrict__ scales, int64_t M, int nwide, int64_t ldx) {
     constexpr int RPB = 256 / TPR;
     const int tid = threadIdx.x;
     const int r_in = tid / TPR;
@@ -67,17 +73,17 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
     const bool live = row < M;
     const __nv_bfloat16* xr = x + row * ldx;
 
-    uint4 v[NCHUNK];
+    Wide v[NW];
     float am = 0.0f;
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
+    for (int i = 0; i < NW; ++i) {
         const int c = t + i * TPR;
-        v[i] = (live && c < nchunks) ? ld_stream16(xr + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
+        v[i] = (live && c < nwide) ? ld_stream32(xr + (int64_t)c * 16) : wide_zero();
     }
     {
-        __nv_bfloat162 pm = amax8_packed(v[0]);
+        __nv_bfloat162 pm = amax16_packed(v[0]);
 #pragma unroll
-        for (int i = 1; i < NCHUNK; ++i) pm = __hmax2(pm, amax8_packed(v[i]));
+        for (int i = 1; i < NW; ++i) pm = __hmax2(pm, amax16_packed(v[i]));
         am = hmax_halves(pm);
     }
     am = warp_max(am);
@@ -93,15 +99,16 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
     const float scale = fmaxf(__fdiv_rn(am, INT8 ? kInt8Max : kFp8Max), kScaleFloor);
     const Divider2 div(scale);
     if (live && t == 0) scales[row] = scale;
-    uint8_t* qr = q + row * ((int64_t)nchunks * 8);
+    uint8_t* qr = q + row * ((int64_t)nwide * 16);
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
+    for (int i = 0; i < NW; ++i) {
         const int c = t + i * TPR;
-        if (live && c < nchunks) *reinterpret_cast<uint2*>(qr + (int64_t)c * 8) = encode8<INT8>(v[i], div);
+        if (live && c < nwide) *reinterpret_cast<uint4*>(qr + (int64_t)c * 16) = encode16<INT8>(v[i], div);
     }
 }
 
-// Rows too long for registers: two passes over global memory (second pass mostly hits L2).
+// Rows too long for registers, or not a multiple of 16 elements / not 32-byte aligned: two
+// passes over global memory in 16-byte chunks (the second pass mostly hits L2).
 template <bool INT8>
 __global__ void __launch_bounds__(256)
 quant_row_long_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
@@ -126,11 +133,11 @@ quant_row_long_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__
 }
 
 template <int NCHUNK, int TPR, bool INT8>
-int launch_row(const void* x, void* q, float* scales, int64_t M, int nchunks, int64_t ldx, cudaStream_t st) {
+int launch_row(const void* x, void* q, float* scales, int64_t M, int nwide, int64_t ldx, cudaStream_t st) {
     constexpr int RPB = 256 / TPR;
     const int64_t grid = (M + RPB - 1) / RPB;
     quant_row_kernel<NCHUNK, TPR, INT8><<<(unsigned)grid, 256, 0, st>>>(
-        (const __nv_bfloat16*)x, (uint8_t*)q, scales, M, nchunks, ldx);
+        (const __nv_bfloat16*)x, (uint8_t*)q, scales, M, nwide, ldx);
     return check_launch("quant_row_kernel");
 }
 
@@ -140,8 +147,7 @@ int dispatch_nchunk(int n, const void* x, void* q, float* scales, int64_t M, int
         case 1: return launch_row<1, TPR, INT8>(x, q, scales, M, nchunks, ldx, st);
         case 2: return launch_row<2, TPR, INT8>(x, q, scales, M, nchunks, ldx, st);
         case 4: return launch_row<4, TPR, INT8>(x, q, scales, M, nchunks, ldx, st);
-        case 8: return launch_row<8, TPR, INT8>(x, q, scales, M, nchunks, ldx, st);
-        default: return launch_row<16, TPR, INT8>(x, q, scales, M, nchunks, ldx, st);
+        default: return launch_row<8, TPR, INT8>(x, q, scales, M, nchunks, ldx, st);
     }
 }
 
@@ -157,29 +163,31 @@ int quant_per_token(const void* x, void* q, float* scales, int64_t M, int64_t D,
     if (M == 0) return HKB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int nchunks = (int)(D / 8);
-    // threads per row: aim at 4 chunks (64 B in flight) per thread
+    // wide path: rows made of whole 32-byte chunks, held in registers (<= 8 chunks = 256 B per thread)
+    const bool wide_ok = D % 16 == 0 && ldx % 16 == 0 && aligned32(x) && aligned16(q);
+    const int nwide = (int)(D / 16);
     int tpr = 32;
-    while (tpr < 256 && tpr * 4 < nchunks) tpr *= 2;
-    int n = (nchunks + tpr - 1) / tpr;
-    if (n > 16) {
+    while (tpr < 256 && tpr * 4 < nwide) tpr *= 2;    // aim at 4 chunks (128 B in flight) per thread
+    const int n = (nwide + tpr - 1) / tpr;
+    if (!wide_ok || n > 8) {
         quant_row_long_kernel<INT8><<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)q, scales, M, nchunks, ldx);
         return check_launch("quant_row_long_kernel");
     }
     int np = 1;
     while (np < n) np *= 2;
     switch (tpr) {
-        case 32: return dispatch_nchunk<32, INT8>(np, x, q, scales, M, nchunks, ldx, st);
-        case 64: return dispatch_nchunk<64, INT8>(np, x, q, scales, M, nchunks, ldx, st);
-        case 128: return dispatch_nchunk<128, INT8>(np, x, q, scales, M, nchunks, ldx, st);
-        default: return dispatch_nchunk<256, INT8>(np, x, q, scales, M, nchunks, ldx, st);
+        case 32: return dispatch_nchunk<32, INT8>(np, x, q, scales, M, nwide, ldx, st);
+        case 64: return dispatch_nchunk<64, INT8>(np, x, q, scales, M, nwide, ldx, st);
+        case 128: return dispatch_nchunk<128, INT8>(np, x, q, scales, M, nwide, ldx, st);
+        default: return dispatch_nchunk<256, INT8>(np, x, q, scales, M, nwide, ldx, st);
     }
 }
 
 // ---- 1x128 -----------------------------------------------------------------------------
 // The [M, D] tensor is a flat sequence of 128-element groups (D % 128 == 0) and the scale
 // array [M, D/128] is the same sequence, so no row structure is needed.  Four lanes own one
-// group: lane (g, s) holds chunks s, s+4, s+8, s+12 of group g, so that every load instruction
-// of a warp covers eight 64-byte runs (full sectors) and the per-group work (amax shuffles,
+// group: lane (g, s) holds the 32-byte chunks s and s+4 of group g, so that every load
+// instruction of a warp covers eight full 128-byte lines and the per-group work (amax shuffles,
 // the divisions that produce scale and reciprocal) is amortised over 32 elements per thread.
 template <int ITER>
 __global__ void __launch_bounds__(256)
@@ -188,27 +196,26 @@ quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 3;
     const int64_t g0 = ((int64_t)blockIdx.x * 8 + warp) * (8 * ITER) + (lane >> 2);
-    uint4 v[ITER][4];
+    Wide v[ITER][2];
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
         const int64_t g = g0 + 8 * it;
-        const __nv_bfloat16* src = x + (g * 16 + sub) * 8;
+        const __nv_bfloat16* src = x + (g * 8 + sub) * 16;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[it][k] = (g < total_groups) ? ld_stream16(src + k * 32) : make_uint4(0, 0, 0, 0);
+        for (int k = 0; k < 2; ++k) v[it][k] = (g < total_groups) ? ld_stream32(src + k * 64) : wide_zero();
     }
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
         const int64_t g = g0 + 8 * it;
-        float am = hmax_halves(__hmax2(__hmax2(amax8_packed(v[it][0]), amax8_packed(v[it][1])),
-                                       __hmax2(amax8_packed(v[it][2]), amax8_packed(v[it][3]))));
+        float am = hmax_halves(__hmax2(amax16_packed(v[it][0]), amax16_packed(v[it][1])));
         am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
         am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 2));
         const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
         const Divider2 div(scale);
         if (g < total_groups) {
-            uint8_t* dst = q + (g * 16 + sub) * 8;
+            uint8_t* dst = q + (g * 8 + sub) * 16;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) *reinterpret_cast<uint2*>(dst + k * 32) = encode8<false>(v[it][k], div);
+            for (int k = 0; k < 2; ++k) *reinterpret_cast<uint4*>(dst + k * 64) = encode16<false>(v[it][k], div);
             if (sub == 0) scales[g] = scale;
         }
     }
@@ -269,22 +276,21 @@ rmsnorm_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
 }
 
 // ---- 128x128 ---------------------------------------------------------------------------
-// One CTA per weight tile; a thread keeps 8 chunks (64 elements) of the 128x128 tile.
+// One CTA per weight tile; a thread keeps four 32-byte chunks (64 elements) of the 128x128 tile.
 __global__ void __launch_bounds__(256)
 quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q,
                      float* __restrict__ scales, int64_t K, int n_tiles) {
     const int kb = blockIdx.x, nb = blockIdx.y;
     const int t = threadIdx.x;
-    uint4 v[8];
-    float am = 0.0f;
+    Wide v[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
         const int j = t + i * 256;
-        const int64_t off = ((int64_t)nb * 128 + (j >> 4)) * K + (int64_t)kb * 128 + (j & 15) * 8;
-        v[i] = ld_stream16(w + off);
+        const int64_t off = ((int64_t)nb * 128 + (j >> 3)) * K + (int64_t)kb * 128 + (j & 7) * 16;
+        v[i] = ld_stream32(w + off);
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) am = fmaxf(am, amax8(v[i]));
+    float am = hmax_halves(__hmax2(__hmax2(amax16_packed(v[0]), amax16_packed(v[1])),
+                                   __hmax2(amax16_packed(v[2]), amax16_packed(v[3]))));
     am = warp_max(am);
     __shared__ float s_am[8];
     if ((t & 31) == 0) s_am[t >> 5] = am;
@@ -296,10 +302,10 @@ quant_128x128_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ 
     const Divider2 div(scale);
     if (t == 0) scales[(int64_t)kb * n_tiles + nb] = scale;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 4; ++i) {
         const int j = t + i * 256;
-        const int64_t off = ((int64_t)nb * 128 + (j >> 4)) * K + (int64_t)kb * 128 + (j & 15) * 8;
-        *reinterpret_cast<uint2*>(q + off) = encode8<false>(v[i], div);
+        const int64_t off = ((int64_t)nb * 128 + (j >> 3)) * K + (int64_t)kb * 128 + (j & 7) * 16;
+        *reinterpret_cast<uint4*>(q + off) = encode16<false>(v[i], div);
     }
 }
 
@@ -320,8 +326,8 @@ int hkb_quant_fp8_1x128(const void* x, const void* w, void* q, float* scales, in
     using namespace hkb;
     HKB_REQUIRE(x && q && scales, HKB_ERR_BAD_ARG, "quant_fp8_1x128: null pointer");
     HKB_REQUIRE(M >= 0 && D > 0 && D % 128 == 0, HKB_ERR_BAD_SHAPE, "quant_fp8_1x128: need D %% 128 == 0, got M=%lld D=%lld", (long long)M, (long long)D);
-    HKB_REQUIRE(aligned16(x) && ((uintptr_t)q & 7) == 0 && ((uintptr_t)scales & 3) == 0 && (!w || aligned16(w)),
-                HKB_ERR_BAD_ALIGN, "quant_fp8_1x128: x/w must be 16-byte, q 8-byte, scales 4-byte aligned");
+    HKB_REQUIRE(aligned32(x) && aligned16(q) && ((uintptr_t)scales & 3) == 0 && (!w || aligned16(w)),
+                HKB_ERR_BAD_ALIGN, "quant_fp8_1x128: x must be 32-byte, q and w 16-byte, scales 4-byte aligned");
     if (M == 0) return HKB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (w) {
@@ -347,8 +353,8 @@ int hkb_quant_fp8_128x128(const void* w, void* q, float* scales, int64_t N, int6
     HKB_REQUIRE(N > 0 && K > 0 && N % 128 == 0 && K % 128 == 0, HKB_ERR_BAD_SHAPE,
                 "quant_fp8_128x128: need N %% 128 == 0 and K %% 128 == 0, got N=%lld K=%lld", (long long)N, (long long)K);
     HKB_REQUIRE(N / 128 <= 65535, HKB_ERR_BAD_SHAPE, "quant_fp8_128x128: N too large");
-    HKB_REQUIRE(aligned16(w) && ((uintptr_t)q & 7) == 0 && ((uintptr_t)scales & 3) == 0, HKB_ERR_BAD_ALIGN,
-                "quant_fp8_128x128: w must be 16-byte, q 8-byte, scales 4-byte aligned");
+    HKB_REQUIRE(aligned32(w) && aligned16(q) && ((uintptr_t)scales & 3) == 0, HKB_ERR_BAD_ALIGN,
+                "quant_fp8_128x128: w must be 32-byte, q 16-byte, scales 4-byte aligned");
     dim3 grid((unsigned)(K / 128), (unsigned)(N / 128));
     quant_128x128_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, (uint8_t*)q, scales, K, (int)(N / 128));
     return check_launch("quant_128x128_kernel");

@@ -3,9 +3,9 @@
 //
 // HBM-bound streaming kernel.  The [M, D] tensor is a flat sequence of 32-element blocks
 // (D % 32 == 0) and the scale array [M, D/32] is the same sequence, so two adjacent lanes own
-// one block (two 16-byte chunks each; a lane pair reads a full 32-byte sector per load): one
-// shuffle gives the block amax, the exponent is read from amax's bit pattern, each lane emits
-// 4 code bytes per chunk and every 8th lane emits four scale bytes as one word.
+// one block (one 32-byte chunk each, a single 256-bit load; a warp reads 1 KB contiguous per
+// load): one shuffle gives the block amax, the exponent is read from amax's bit pattern, each
+// lane emits 8 code bytes and every 8th lane emits four scale bytes as one word.
 //
 // Rounding rule of mode 0: nearest E2M1 magnitude of x / 2^e with ties to the SMALLER
 // magnitude, saturating at 6; sign nibble set iff x < 0.  For bf16 inputs x / 2^e carries at
@@ -89,8 +89,8 @@ __device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
     }
 }
 
-// Two adjacent lanes own one 32-element block: lane (b, h) holds chunks 2k + h (k = 0, 1) of
-// block b.  A warp covers 16 blocks per iteration, a thread keeps 2 * ITER chunks in flight.
+// Two adjacent lanes own one 32-element block: lane (b, h) holds elements [16h, 16h+16) of
+// block b.  A warp covers 16 blocks per iteration, a thread keeps ITER 32-byte chunks in flight.
 template <int MODE, int ITER>
 __global__ void __launch_bounds__(256)
 quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ codes,
@@ -98,29 +98,23 @@ quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = lane & 1;
     const int64_t b0 = ((int64_t)blockIdx.x * 8 + warp) * (16 * ITER) + (lane >> 1);
-    uint4 v[ITER][2];
+    Wide v[ITER];
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
         const int64_t b = b0 + 16 * it;
-        const __nv_bfloat16* src = x + (b * 4 + h) * 8;
-#pragma unroll
-        for (int k = 0; k < 2; ++k) v[it][k] = (b < total_blocks) ? ld_stream16(src + k * 16) : make_uint4(0, 0, 0, 0);
+        v[it] = (b < total_blocks) ? ld_stream32(x + (b * 2 + h) * 16) : wide_zero();
     }
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
         const int64_t b = b0 + 16 * it;
-        float am = hmax_halves(__hmax2(amax8_packed(v[it][0]), amax8_packed(v[it][1])));
+        float am = hmax_halves(amax16_packed(v[it]));
         am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
         uint32_t sb;
         float inv;
         block_exponent<MODE>(am, sb, inv);
-        const uint32_t c0 = encode8_bf16<MODE>(v[it][0], inv);
-        const uint32_t c1 = encode8_bf16<MODE>(v[it][1], inv);
-        if (b < total_blocks) {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(codes + (b * 4 + h) * 4);
-            dst[0] = c0;
-            dst[2] = c1;
-        }
+        const uint32_t c0 = encode8_bf16<MODE>(v[it].lo, inv);
+        const uint32_t c1 = encode8_bf16<MODE>(v[it].hi, inv);
+        if (b < total_blocks) *reinterpret_cast<uint2*>(codes + (b * 2 + h) * 8) = make_uint2(c0, c1);
         // scale bytes of 4 consecutive blocks (lanes 8j, 8j+2, 8j+4, 8j+6) go out as one word
         const int l8 = lane & 24;
         const uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, l8) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 2) << 8) |
@@ -204,8 +198,8 @@ extern "C" int hkb_quant_mxfp4(const void* x, const void* w, void* codes, void* 
     HKB_REQUIRE(x && codes && scales, HKB_ERR_BAD_ARG, "quant_mxfp4: null pointer");
     HKB_REQUIRE(mode == HKB_MXFP4_MODE_DOC || mode == HKB_MXFP4_MODE_KERNEL, HKB_ERR_BAD_ARG, "quant_mxfp4: unknown mode %d", mode);
     HKB_REQUIRE(M >= 0 && D > 0 && D % 32 == 0, HKB_ERR_BAD_SHAPE, "quant_mxfp4: need D %% 32 == 0, got M=%lld D=%lld", (long long)M, (long long)D);
-    HKB_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3) == 0 && ((uintptr_t)scales & 3) == 0 && (!w || aligned16(w)),
-                HKB_ERR_BAD_ALIGN, "quant_mxfp4: x/w must be 16-byte, codes and scales 4-byte aligned");
+    HKB_REQUIRE(aligned32(x) && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)scales & 3) == 0 && (!w || aligned16(w)),
+                HKB_ERR_BAD_ALIGN, "quant_mxfp4: x must be 32-byte, w 16-byte, codes 8-byte, scales 4-byte aligned");
     if (M == 0) return HKB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (w) {

@@ -15,6 +15,8 @@ synthetic tensors, there is no dataset behind this metric):
   c4a  per-token FP8, M=16 N=28672 K=8192 (decode shape, HBM-bound)
   c4b  batched per-token FP8, B=8 M=512 N=4096 K=4096
   c1   per-token FP8, M=128 N=1024 K=1024 (latency-bound parity configuration)
+  p8k  per-token FP8, M=N=K=8192 (tuning shape, not a benchmark configuration)
+  p2   per-token FP8 on config 2's shape (tuning shape: isolates the block-scale promotion cost)
   qbw-fp8 / qbw-1x128 / qbw-mxfp4   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192)
 
 `value` is device time with inputs resident in HBM (CUDA events per step on the launching
@@ -45,6 +47,8 @@ WORKLOADS = {
     "c4a": ("pts", 1, 16, 28672, 8192),
     "c4b": ("pts", 8, 512, 4096, 4096),
     "c5": ("blockscale", 1, 16384, 57344, 8192),
+    "p8k": ("pts", 1, 8192, 8192, 8192),
+    "p2": ("pts", 1, 4096, 14336, 4096),
     "qbw-fp8": ("quant-fp8", 1, 16384, 0, 8192),
     "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
     "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),

@@ -44,7 +44,8 @@ int hkb_check_status(void* stream);
 /* ---- quantizers ---------------------------------------------------------------------- */
 
 /* Per-row dynamic FP8: scales[m] = max(amax_m / 448, 1e-10), q = e4m3fn(clamp(x / scale)).
- * x bf16 [M, D] with row pitch ldx elements; q u8 [M, D]; scales f32 [M].  D % 8 == 0.
+ * x bf16 [M, D] with row pitch ldx elements; q u8 [M, D]; scales f32 [M].  D % 8 == 0; x 16-byte
+ * and q 8-byte aligned (fast path: D % 16 == 0, ldx % 16 == 0, x 32-byte and q 16-byte aligned).
  * Replaces per_token_quant_fwd(input, output, scales):
  *   kernels/quantization/quant/kernel.cpp:31-109,159-171 (re-targeted from INT8/127 to e4m3fn/448). */
 int hkb_quant_fp8_per_token(const void* x, void* q, float* scales,
@@ -57,19 +58,22 @@ int hkb_quant_int8_per_token(const void* x, void* q, float* scales,
 
 /* 1x128 block FP8: one fp32 scale per 128 contiguous columns, scales f32 [M, D/128].
  * w (bf16 [D]) non-null selects the fused RMSNorm prologue y = x*rsqrt(mean x^2+eps)*w.
+ * x 32-byte, q and w 16-byte aligned.
  * Replaces fused_rmsnorm_fp8_quant_fwd(input, weight, output, scales, eps):
  *   kernels/quantization/fused_fp8_quant/kernel.cpp:110-210,262-275. */
 int hkb_quant_fp8_1x128(const void* x, const void* w_or_null, void* q, float* scales,
                         int64_t M, int64_t D, float eps, void* stream);
 
 /* 128x128 block FP8 for weights: w bf16 [N, K] -> q u8 [N, K], scales f32 [K/128, N/128]
- * (transposed, the b_scale layout of the block-scale GEMM).  No reference kernel; produces
+ * (transposed, the b_scale layout of the block-scale GEMM); w 32-byte, q 16-byte aligned.
+ * No reference kernel; produces
  * the operand layout of kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:7,41,146. */
 int hkb_quant_fp8_128x128(const void* w, void* q, float* scales,
                           int64_t N, int64_t K, void* stream);
 
 /* MXFP4: e2m1 codes packed 2/byte (element 2i in the low nibble), one e8m0 byte per 32
- * contiguous elements.  codes u8 [M, D/2], scales u8 [M, D/32].  D % 32 == 0.
+ * contiguous elements.  codes u8 [M, D/2], scales u8 [M, D/32].  D % 32 == 0; x 32-byte,
+ * codes 8-byte, scales 4-byte aligned.
  * Replaces fused_rmsnorm_mxfp4_quant_fwd(input, weight, output, scales, eps):
  *   kernels/quantization/fused_mxfp4_quant/kernel.cpp:71-169,172-249,301-314. */
 int hkb_quant_mxfp4(const void* x, const void* w_or_null, void* codes, void* scales,
