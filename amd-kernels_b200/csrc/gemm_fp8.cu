@@ -81,17 +81,23 @@ struct GemmParams {
 
 // kPair: two CTAs (a cluster of 2) share one 256 x BN tile; each stages its own 128 rows of A
 // and its own half of B's BN rows.
-template <int BN, int STAGES, bool kPair = false>
+// AROWS < 128 (skinny-M problems): only AROWS rows of A are staged per stage, which frees smem
+// for more stages (more weight bytes in flight).  The MMA still reads 128 rows from the A base,
+// i.e. it runs on into whatever follows; those rows only feed accumulator rows >= M, which are
+// never stored.  kTailPad keeps that overrun of the last stage inside the allocation.
+template <int BN, int STAGES, bool kPair = false, int AROWS = BM>
 struct SmemLayout {
-    static constexpr int kABytes = BM * BK;
+    static constexpr int kABytes = AROWS * BK;
+    static constexpr int kTailPad = (BM - AROWS) * BK;
     static constexpr int kBRows = kPair ? BN / 2 : BN;
     static constexpr int kBBytes = kBRows * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = STAGES * kStageBytes;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
     static constexpr int kNumBars = 2 * STAGES + 4;
-    static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+    static constexpr int kTotal = kBarOffset + (kNumBars * 8 + 16 > kTailPad ? kNumBars * 8 + 16 : kTailPad);
     static constexpr int kDynamic = kTotal + 1024;   // slack for the manual 1024-byte alignment
+    static_assert(kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
 __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* dst, const float* v) {
@@ -140,10 +146,10 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
     return __ffma2_rn(make_float2(__uint_as_float(a0), __uint_as_float(a1)), s, c);
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false>
+template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM>
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-    using L = SmemLayout<BN, STAGES, kPair>;
+    using L = SmemLayout<BN, STAGES, kPair, AROWS>;
     static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
     constexpr int EPI_WARPS = 4 * EPI_GROUPS;
@@ -489,10 +495,10 @@ inline bool pairs_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false>
+template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
-    using L = SmemLayout<BN, STAGES>;
-    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128>;
+    using L = SmemLayout<BN, STAGES, false, AROWS>;
+    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS>;
     // the attribute is per device; set it on every call (cheap) so multi-device processes work
     const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     HKB_REQUIRE(attr_err == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(attr_err));
@@ -559,6 +565,9 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
     if (rc != HKB_OK) return rc;
     if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, p, st);
     if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, p, st);
+    // skinny M with narrow tiles (decode shapes): stage only the A rows that exist, deepen the ring
+    if (p.a_box_rows <= 16) return launch_gemm<64, 19, false, false, 16>(tmA, tmB, p, st);
+    if (p.a_box_rows <= 64) return launch_gemm<64, 12, false, false, 64>(tmA, tmB, p, st);
     return launch_gemm<64, 8, false>(tmA, tmB, p, st);
 }
 

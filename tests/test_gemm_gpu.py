@@ -77,7 +77,7 @@ def _dev(a, dtype=None):
 
 @pytest.mark.parametrize("shape", [(128, 128, 128), (512, 512, 512), (2048, 2048, 2048),   # the reference's sizes
                                    (128, 1024, 1024), (200, 1032, 384), (16, 2048, 1024), (1, 256, 128),
-                                   (384, 4608, 512)])
+                                   (48, 512, 2560), (72, 640, 256), (384, 4608, 512)])
 def test_gemm_per_token_scale(hk, shape):
     M, N, K = shape
     aq, bq, sa, sb = _fp8_operands(M, N, K)
