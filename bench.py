@@ -58,7 +58,13 @@ L2_FLUSH_BYTES = 256 << 20
 
 # DRAM bytes (read + write) of ONE launch of the dominant kernel from an ncu capture, per workload
 # (profiles/ has the captures); None = not captured.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    "c2": 290.1e6,       # profiles/c2_gemm_fp8_blockscale.md
+    "c3": 191.7e6,       # profiles/c3_gemm_mxfp4.md
+    "c4a": 239.4e6,      # profiles/c4a_gemm_fp8_decode.md
+    "c4b": 166.3e6,      # profiles/c4b_gemm_fp8_per_token_pairs.md
+    "qbw-fp8": 373.3e6,  # profiles/qbw_quant_per_token_fp8.md
+}
 
 
 def load_peaks():
@@ -389,6 +395,11 @@ def default_sample_rows(name):
 
 
 def run_reference(args, name, world):
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core it may run on
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     kind, B, M, N, K = WORKLOADS[name]
     rows = default_sample_rows(name)
     for _ in range(args.warmup):
