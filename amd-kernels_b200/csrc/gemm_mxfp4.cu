@@ -20,9 +20,7 @@ namespace hkb {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BN = 128;
 constexpr int BKB = 128;          // bytes of K per stage (= 256 e2m1 elements)
-constexpr int STAGES = 6;
 constexpr int GROUP_M = 8;
 constexpr int SF_STAGE = 1024;    // scale bytes per 128 rows per stage (two atoms)
 
@@ -30,8 +28,9 @@ struct Mxfp4Params {
     int M, N, K, batch;
     int m_blks, n_blks;
     int katoms;                   // atoms per 128-row block in the scratch: K / 128 rounded up to even
+    int sfb_rblks;                // 128-row blocks of B's scales per batch in the scratch (incl. zero padding)
     const uint8_t* sfa;           // re-laid-out scales of A: [batch, m_blks, katoms, 512]
-    const uint8_t* sfb;           // re-laid-out scales of B: [batch, n_blks, katoms, 512]
+    const uint8_t* sfb;           // re-laid-out scales of B: [batch, sfb_rblks, katoms, 512]
     __nv_bfloat16* C;
     uint32_t* status;
 };
@@ -67,23 +66,41 @@ sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, i
     }
 }
 
-struct Smem {
+// Tile width.  The tensor core reads a K=64 slice of both operand tiles from shared memory per
+// MMA, so a 128-wide tile saturates that path at ~63 % tensor activity; wider is better, but two
+// accumulators of BN columns plus the scale factors must fit the 512 TMEM columns, which rules
+// out 256.  192 = 6 x 32 columns works: 2 x 192 + 8 (SFA) + 16 (SFB) = 408.  A 192-wide tile
+// starts 0 or 64 rows into a 128-row scale atom of B, so two atoms are staged per K atom and the
+// MMA's scale-factor address is advanced by 0 or 2 TMEM columns (one column = 32 rows) to the
+// tile's first row group.  (The offset has to stay even: a 224-wide tile, whose offsets are
+// 0..3 columns, faulted with "misaligned address".)
+template <int BN>
+struct Cfg {
+    static_assert(BN == 128 || BN == 192, "supported tile widths");
+    static constexpr int kStages = BN == 128 ? 6 : 5;
+    static constexpr int kSfbAtoms = BN == 128 ? 1 : 2;            // 128-row scale atoms staged per K atom
     static constexpr int kABytes = BM * BKB;
     static constexpr int kBBytes = BN * BKB;
     static constexpr int kSfaOff = kABytes + kBBytes;
     static constexpr int kSfbOff = kSfaOff + SF_STAGE;
-    static constexpr int kStageBytes = kSfbOff + SF_STAGE;        // 34 KB, a multiple of 1024
-    static constexpr int kBarOffset = STAGES * kStageBytes;
-    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kStageBytes = kSfbOff + kSfbAtoms * SF_STAGE;   // 34 KB / 43 KB, multiples of 1024
+    static constexpr int kBarOffset = kStages * kStageBytes;
+    static constexpr int kNumBars = 2 * kStages + 4;
     static constexpr int kDynamic = kBarOffset + kNumBars * 8 + 16 + 1024;
+    static constexpr uint32_t kTmemCols = 512;                     // power of two >= 2*BN + 8 + 8*kSfbAtoms
+    static constexpr uint32_t kTmemSfa = 2 * BN;
+    static constexpr uint32_t kTmemSfb = 2 * BN + 8;
+    static_assert(kTmemSfb + 8 * kSfbAtoms <= 512, "TMEM budget");
+    static_assert(kDynamic <= 232448, "shared memory budget");
 };
 
-constexpr uint32_t TMEM_COLS = 512;               // 2 x 128 accumulator + 8 + 8 scale columns, power of two
-constexpr uint32_t TMEM_SFA = 2 * BN;             // columns [256, 264)
-constexpr uint32_t TMEM_SFB = 2 * BN + 8;         // columns [264, 272)
-
+template <int BN>
 __global__ void __launch_bounds__(192, 1)
 gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Mxfp4Params p) {
+    using Smem = Cfg<BN>;
+    constexpr int STAGES = Smem::kStages;
+    constexpr uint32_t TMEM_COLS = Smem::kTmemCols, TMEM_SFA = Smem::kTmemSfa, TMEM_SFB = Smem::kTmemSfb;
+    constexpr int SFB_ATOMS = Smem::kSfbAtoms;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -123,7 +140,7 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (elect_one()) {
             prefetch_tmap(&tmA);
             prefetch_tmap(&tmB);
-            constexpr uint32_t stage_tx = Smem::kABytes + Smem::kBBytes + 2 * SF_STAGE;
+            constexpr uint32_t stage_tx = Smem::kABytes + Smem::kBBytes + (1 + SFB_ATOMS) * SF_STAGE;
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -132,7 +149,9 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 int mb, nb;
                 tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
                 const uint8_t* sfa_row = p.sfa + ((int64_t)b * p.m_blks + mb) * p.katoms * 512;
-                const uint8_t* sfb_row = p.sfb + ((int64_t)b * p.n_blks + nb) * p.katoms * 512;
+                // first 128-row scale atom that the tile's B rows touch
+                const int atom0 = (nb * BN) >> 7;
+                const uint8_t* sfb_row = p.sfb + ((int64_t)b * p.sfb_rblks + atom0) * p.katoms * 512;
                 for (int ks = 0; ks < kstages; ++ks) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
                     mbar_arrive_expect_tx(full_bar(s), stage_tx);
@@ -140,7 +159,10 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     tma_load_3d(st, &tmA, full_bar(s), ks * BKB, mb * BM, b);
                     tma_load_3d(st + Smem::kABytes, &tmB, full_bar(s), ks * BKB, nb * BN, b);
                     bulk_load(st + Smem::kSfaOff, sfa_row + (int64_t)ks * SF_STAGE, SF_STAGE, full_bar(s));
-                    bulk_load(st + Smem::kSfbOff, sfb_row + (int64_t)ks * SF_STAGE, SF_STAGE, full_bar(s));
+#pragma unroll
+                    for (int r = 0; r < SFB_ATOMS; ++r)
+                        bulk_load(st + Smem::kSfbOff + r * SF_STAGE, sfb_row + ((int64_t)r * p.katoms * 512) + (int64_t)ks * SF_STAGE,
+                                  SF_STAGE, full_bar(s));
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
@@ -156,6 +178,14 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                // 32-row group inside the first staged scale atom at which this tile's B rows start
+                int sf_off = 0;
+                if constexpr (SFB_ATOMS > 1) {
+                    const int b_ = t / tiles_per_batch;
+                    int mb_, nb_;
+                    tile_coords(t - b_ * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb_, nb_);
+                    sf_off = ((nb_ * BN) >> 5) & 3;          // 0 or 2 for BN = 192
+                }
                 for (int ks = 0; ks < kstages; ++ks) {
                     if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
                     tc_fence_after();
@@ -165,13 +195,16 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {      // the two 128-K atoms of this stage
                         tc_cp_sf(tmem_base + TMEM_SFA + h * 4, smem_desc_sf(st + Smem::kSfaOff + h * 512));
-                        tc_cp_sf(tmem_base + TMEM_SFB + h * 4, smem_desc_sf(st + Smem::kSfbOff + h * 512));
+#pragma unroll
+                        for (int r = 0; r < SFB_ATOMS; ++r)
+                            tc_cp_sf(tmem_base + TMEM_SFB + (h * SFB_ATOMS + r) * 4,
+                                     smem_desc_sf(st + Smem::kSfbOff + r * SF_STAGE + h * 512));
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {      // 4 x K=64 (32 bytes of each 128-byte row)
                         const uint32_t h = k >> 1, sf_id = (k & 1) * 2;
                         mma_mxf4(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_mxf4(BM, BN, sf_id, sf_id),
-                                 tmem_base + TMEM_SFA + h * 4, tmem_base + TMEM_SFB + h * 4, (ks | k) != 0);
+                                 tmem_base + TMEM_SFA + h * 4, tmem_base + TMEM_SFB + h * SFB_ATOMS * 4 + sf_off, (ks | k) != 0);
                     }
                     tc_commit(empty_bar(s));
                     if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -258,7 +291,14 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
     Mxfp4Params p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.m_blks = (int)((M + BM - 1) / BM);
-    p.n_blks = (int)((N + BN - 1) / BN);
+    // wide tiles when there are enough of them to fill the SMs twice over
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
+    const bool wide = (int64_t)p.m_blks * ((N + 191) / 192) * batch >= 2LL * sms;
+    const int bn = wide ? 192 : 128;
+    p.n_blks = (int)((N + bn - 1) / bn);
+    const int n_atoms = (int)((N + 127) / 128);
+    p.sfb_rblks = n_atoms + (wide ? 2 : 0);          // wide tiles may stage up to two atoms past the last one
     const int katoms_src = (int)(K / 128);
     p.katoms = (katoms_src + 1) & ~1;
     p.C = (__nv_bfloat16*)C;
@@ -268,7 +308,7 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
     // scale re-layout into library-owned scratch (grown on demand, reused across calls)
     void *sfa_sw = nullptr, *sfb_sw = nullptr;
     const size_t sfa_bytes = (size_t)batch * p.m_blks * p.katoms * 512;
-    const size_t sfb_bytes = (size_t)batch * p.n_blks * p.katoms * 512;
+    const size_t sfb_bytes = (size_t)batch * p.sfb_rblks * p.katoms * 512;
     rc = scratch_get(SCRATCH_SFA, sfa_bytes, &sfa_sw);
     if (rc != HKB_OK) return rc;
     rc = scratch_get(SCRATCH_SFB, sfb_bytes, &sfb_sw);
@@ -276,8 +316,8 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
     {
         dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)p.m_blks, (unsigned)batch);
         sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)sfa, (uint8_t*)sfa_sw, (int)M, katoms_src, p.katoms, p.m_blks);
-        dim3 gb((unsigned)((p.katoms + 31) / 32), (unsigned)p.n_blks, (unsigned)batch);
-        sf_relayout_kernel<<<gb, 256, 0, st>>>((const uint8_t*)sfb, (uint8_t*)sfb_sw, (int)N, katoms_src, p.katoms, p.n_blks);
+        dim3 gb((unsigned)((p.katoms + 31) / 32), (unsigned)p.sfb_rblks, (unsigned)batch);
+        sf_relayout_kernel<<<gb, 256, 0, st>>>((const uint8_t*)sfb, (uint8_t*)sfb_sw, (int)N, katoms_src, p.katoms, p.sfb_rblks);
         rc = check_launch("sf_relayout_kernel");
         if (rc != HKB_OK) return rc;
     }
@@ -287,14 +327,19 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
     CUtensorMap tmA, tmB;
     rc = make_tmap_bytes(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)batch, BM);
     if (rc != HKB_OK) return rc;
-    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, BN);
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
-    const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
-    HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     const int tiles = p.m_blks * p.n_blks * p.batch;
-    const int sms = sm_count();
-    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
-    gemm_mxfp4_kernel<<<tiles < sms ? tiles : sms, 192, Smem::kDynamic, st>>>(tmA, tmB, p);
+    const int grid = tiles < sms ? tiles : sms;
+    if (wide) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<192>::kDynamic);
+        HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+        gemm_mxfp4_kernel<192><<<grid, 192, Cfg<192>::kDynamic, st>>>(tmA, tmB, p);
+    } else {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::kDynamic);
+        HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+        gemm_mxfp4_kernel<128><<<grid, 192, Cfg<128>::kDynamic, st>>>(tmA, tmB, p);
+    }
     return check_launch("gemm_mxfp4_kernel");
 }
 
@@ -349,7 +394,7 @@ int static_addresses(StaticSlot* out) {
         // In host code the array names are host-side handles, not device addresses: ask the runtime.
         HKB_CUDA(cudaGetSymbolAddress(&p, g_static_sf));
         HKB_CUDA(cudaGetSymbolAddress(&q, g_static_status));
-        HKB_CUDA(cudaFuncSetAttribute(gemm_mxfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic));
+        HKB_CUDA(cudaFuncSetAttribute(gemm_mxfp4_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::kDynamic));
         s.status = static_cast<uint32_t*>(q);
         s.sf = static_cast<uint8_t*>(p);
     }
@@ -374,7 +419,8 @@ extern "C" int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, cons
     Mxfp4Params p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.m_blks = (int)((M + BM - 1) / BM);
-    p.n_blks = (int)((N + BN - 1) / BN);
+    p.n_blks = (int)((N + 127) / 128);
+    p.sfb_rblks = p.n_blks;
     const int katoms_src = (int)(K / 128);
     p.katoms = (katoms_src + 1) & ~1;
     p.C = (__nv_bfloat16*)C;
@@ -403,11 +449,11 @@ extern "C" int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, cons
     CUtensorMap tmA, tmB;
     rc = make_tmap_bytes(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)batch, BM);
     if (rc != HKB_OK) return rc;
-    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, BN);
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, 128);
     if (rc != HKB_OK) return rc;
     const int tiles = p.m_blks * p.n_blks * p.batch;
     const int sms = sm_count();
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
-    gemm_mxfp4_kernel<<<tiles < sms ? tiles : sms, 192, Smem::kDynamic, st>>>(tmA, tmB, p);
+    gemm_mxfp4_kernel<128><<<tiles < sms ? tiles : sms, 192, Cfg<128>::kDynamic, st>>>(tmA, tmB, p);
     return check_launch("gemm_mxfp4_kernel");
 }
