@@ -153,10 +153,8 @@ struct Divider2 {
 
 // max |.| over the 8 bf16 of a chunk as a packed bf16 pair (both halves hold partial maxima)
 __device__ __forceinline__ __nv_bfloat162 amax8_packed(const uint4& v) {
-    const uint32_t m = 0x7FFF7FFFu;
-    uint32_t x0 = v.x & m, x1 = v.y & m, x2 = v.z & m, x3 = v.w & m;
-    return __hmax2(__hmax2(*reinterpret_cast<__nv_bfloat162*>(&x0), *reinterpret_cast<__nv_bfloat162*>(&x1)),
-                   __hmax2(*reinterpret_cast<__nv_bfloat162*>(&x2), *reinterpret_cast<__nv_bfloat162*>(&x3)));
+    auto h2 = [](const uint32_t& w) { return __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w)); };
+    return __hmax2(__hmax2(h2(v.x), h2(v.y)), __hmax2(h2(v.z), h2(v.w)));
 }
 __device__ __forceinline__ __nv_bfloat162 amax16_packed(const Wide& v) { return __hmax2(amax8_packed(v.lo), amax8_packed(v.hi)); }
 __device__ __forceinline__ float hmax_halves(__nv_bfloat162 m) { return fmaxf(__low2float(m), __high2float(m)); }

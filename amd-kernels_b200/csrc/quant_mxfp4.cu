@@ -8,27 +8,28 @@
 // lane emits 8 code bytes and every 8th lane emits four scale bytes as one word.
 //
 // Rounding rule of mode 0: nearest E2M1 magnitude of x / 2^e with ties to the SMALLER
-// magnitude, saturating at 6; sign nibble set iff x < 0.  For bf16 inputs x / 2^e carries at
-// most 8 significant bits, so subtracting 2^-12 from |q| turns every tie into a non-tie
-// without moving any other value across a rounding boundary; the hardware round-to-nearest
-// conversion (cvt.rn.satfinite.relu.e2m1x2.f32 on |q| - 2^-12; relu turns the slightly negative
-// results of tiny inputs into +0) then yields exactly that rule.  fp32 inputs (the RMSNorm
-// prologue) and mode 1 (truncation) use explicit threshold compares.
+// magnitude, saturating at 6; sign nibble set iff x < 0.  For bf16 inputs q = x / 2^e carries at
+// most 8 significant bits, so shrinking it by the factor (1 - 2^-10) turns every tie into a
+// non-tie without moving any other value across a rounding boundary (a value above a boundary
+// is at least one 8-bit grid step = |q| * 2^-8 away from it).  The hardware round-to-nearest
+// conversion (cvt.rn.satfinite.e2m1x2.f32) of q' = fma(x, 2^-e * (1 - 2^-10), +0) then yields
+// exactly that rule, sign included: the conversion keeps the sign of results that round to
+// zero, and the "+0" addend turns the product of x = -0.0 into +0 ("x < 0" is false for it).
+// fp32 inputs (the RMSNorm prologue) and mode 1 (truncation) use explicit threshold compares.
 #include "common.cuh"
 
 namespace hkb {
 namespace {
 
 // eight floats -> eight e2m1 nibbles in one word, element j in bits 4j..4j+3
-// (negative inputs give +0: callers pass magnitudes and add the sign bits themselves)
 __device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&r)[8]) {
     uint32_t o;
     asm("{\n"
         ".reg .b8 b0, b1, b2, b3;\n"
-        "cvt.rn.satfinite.relu.e2m1x2.f32 b0, %2, %1;\n"
-        "cvt.rn.satfinite.relu.e2m1x2.f32 b1, %4, %3;\n"
-        "cvt.rn.satfinite.relu.e2m1x2.f32 b2, %6, %5;\n"
-        "cvt.rn.satfinite.relu.e2m1x2.f32 b3, %8, %7;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
         "mov.b32 %0, {b0, b1, b2, b3};\n"
         "}"
         : "=r"(o)
@@ -71,21 +72,14 @@ __device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
         for (int j = 0; j < 8; ++j) o |= nibble_compare(f[j] * inv, MODE) << (4 * j);
         return o;
     } else {
-        // |x| * 2^-e - 2^-12 on the packed fp32 pipe, magnitudes straight from the masked bf16 bits
-        const float2 inv2 = make_float2(inv, inv), nd2 = make_float2(-0x1p-12f, -0x1p-12f);
-        const float2 m0 = __ffma2_rn(bf16x2_to_f2(v.x & 0x7FFF7FFFu), inv2, nd2);
-        const float2 m1 = __ffma2_rn(bf16x2_to_f2(v.y & 0x7FFF7FFFu), inv2, nd2);
-        const float2 m2 = __ffma2_rn(bf16x2_to_f2(v.z & 0x7FFF7FFFu), inv2, nd2);
-        const float2 m3 = __ffma2_rn(bf16x2_to_f2(v.w & 0x7FFF7FFFu), inv2, nd2);
+        // x * (2^-e * (1 - 2^-10)) + 0 on the packed fp32 pipe; `inv` already carries the factor
+        const float2 inv2 = make_float2(inv, inv), z2 = make_float2(0.0f, 0.0f);
+        const float2 m0 = __ffma2_rn(bf16x2_to_f2(v.x), inv2, z2);
+        const float2 m1 = __ffma2_rn(bf16x2_to_f2(v.y), inv2, z2);
+        const float2 m2 = __ffma2_rn(bf16x2_to_f2(v.z), inv2, z2);
+        const float2 m3 = __ffma2_rn(bf16x2_to_f2(v.w), inv2, z2);
         const float r[8] = {m0.x, m0.y, m1.x, m1.y, m2.x, m2.y, m3.x, m3.y};
-        // sign nibble bit = "x < 0" = sign bit set and magnitude non-zero, from the bf16 bits
-        // themselves (a product that underflows to zero must still carry it)
-        auto sgn = [](uint32_t w) {
-            const uint32_t nz = (w & 0x7FFF7FFFu) + 0x7FFF7FFFu;      // bit 15 / 31 set iff that half is non-zero
-            const uint32_t m = nz & w & 0x80008000u;
-            return ((m >> 12) & 0x8u) | ((m >> 24) & 0x80u);
-        };
-        return cvt_e2m1x8(r) | sgn(v.x) | (sgn(v.y) << 8) | (sgn(v.z) << 16) | (sgn(v.w) << 24);
+        return cvt_e2m1x8(r);
     }
 }
 
@@ -112,6 +106,7 @@ quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ co
         uint32_t sb;
         float inv;
         block_exponent<MODE>(am, sb, inv);
+        if constexpr (MODE == HKB_MXFP4_MODE_DOC) inv *= (1.0f - 0x1p-10f);     // exact: inv is a power of two
         const uint32_t c0 = encode8_bf16<MODE>(v[it].lo, inv);
         const uint32_t c1 = encode8_bf16<MODE>(v[it].hi, inv);
         if (b < total_blocks) *reinterpret_cast<uint2*>(codes + (b * 2 + h) * 8) = make_uint2(c0, c1);

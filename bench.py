@@ -17,7 +17,7 @@ synthetic tensors, there is no dataset behind this metric):
   c1   per-token FP8, M=128 N=1024 K=1024 (latency-bound parity configuration)
   p8k  per-token FP8, M=N=K=8192 (tuning shape, not a benchmark configuration)
   p2   per-token FP8 on config 2's shape (tuning shape: isolates the block-scale promotion cost)
-  qbw-fp8 / qbw-1x128 / qbw-mxfp4   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192)
+  qbw-fp8 / qbw-1x128 / qbw-mxfp4 / qbw-mxfp4-16k   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192, 16384x8192)
 
 `value` is device time with inputs resident in HBM (CUDA events per step on the launching
 stream, L2 flushed between steps, max over ranks); `e2e` is the same metric through the public
@@ -52,6 +52,7 @@ WORKLOADS = {
     "qbw-fp8": ("quant-fp8", 1, 16384, 0, 8192),
     "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
     "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),
+    "qbw-mxfp4-16k": ("quant-mxfp4", 1, 16384, 0, 8192),
 }
 METRIC = "quant GEMM TFLOPS & % of FP8/FP4 tensor peak; quantizer GB/s vs HBM peak"
 L2_FLUSH_BYTES = 256 << 20
