@@ -35,10 +35,7 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
 std::once_flag g_encode_once;
-}  // namespace
-
-int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
-                    uint64_t batch, uint32_t box_rows) {
+void load_encoder() {
     std::call_once(g_encode_once, [] {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -46,6 +43,12 @@ int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint
             q == cudaDriverEntryPointSuccess)
             g_encode = reinterpret_cast<EncodeFn>(fn);
     });
+}
+}  // namespace
+
+int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
+                    uint64_t batch, uint32_t box_rows) {
+    load_encoder();
     HKB_REQUIRE(g_encode != nullptr, HKB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     HKB_REQUIRE(aligned16(base) && row_bytes % 16 == 0, HKB_ERR_BAD_ALIGN,
                 "TMA operands need a 16-byte aligned base and row pitch (pitch %llu bytes)", (unsigned long long)row_bytes);
@@ -495,6 +498,11 @@ inline bool pairs_enabled() {
     return on;
 }
 
+inline bool skinny_enabled() {
+    static const bool on = [] { const char* v = getenv("HKB_GEMM_SKINNY"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
 template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
     using L = SmemLayout<BN, STAGES, false, AROWS>;
@@ -537,6 +545,10 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
     p.sa = sa; p.sb = sb; p.bias = (const __nv_bfloat16*)bias; p.C = (__nv_bfloat16*)C; p.gn = 0;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
+    // Decode shapes: HBM-bound on the weight stream; a kernel that deals the columns out evenly
+    // over the SMs (gemm_fp8_skinny.cu).  HKB_GEMM_SKINNY=0 keeps the fixed-width tiles below.
+    if (M <= 64 && batch == 1 && N % 16 == 0 && aligned32(C) && aligned16(sb) && (!bias || aligned16(bias)) && skinny_enabled())
+        return launch_gemm_fp8_skinny(A, B, C, sa, sb, bias, M, N, K, p.status, (cudaStream_t)stream);
     p.m_blks = (int)((M + BM - 1) / BM);
     // Skinny M: fetch only the rows that exist (rounded up to 8); the remaining rows of the
     // smem tile hold stale bytes that only reach accumulator rows >= M, which are never stored.

@@ -15,6 +15,11 @@ namespace hkb {
 int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
                     uint64_t batch, uint32_t box_rows);
 
+// Per-token-scale FP8 GEMM for M <= 64, batch 1, N % 16 == 0 (gemm_fp8_skinny.cu); arguments are
+// expected to be validated by the caller.  `status` is the device status word.
+int launch_gemm_fp8_skinny(const void* A, const void* B, void* C, const float* sa, const float* sb, const void* bias,
+                           int64_t M, int64_t N, int64_t K, uint32_t* status, cudaStream_t st);
+
 // ---- device --------------------------------------------------------------------------------
 constexpr uint32_t kErrWaitProducer = 1u;   // status bits OR-ed into the device status word
 constexpr uint32_t kErrWaitMma = 2u;
@@ -127,6 +132,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+// 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }

@@ -172,6 +172,36 @@ def test_decode_shape_sampled_columns(hk):
     cols = torch.randperm(N, generator=torch.Generator().manual_seed(0))[:1024].sort().values
     ref = gemm.gemm_fp8_per_token(aq.cpu(), wq[cols.to(DEV)].cpu(), sa.cpu(), sw[cols.to(DEV)].cpu())
     _check(C[:, cols.to(DEV)], ref, "decode sampled columns")
+    # every column (all tile widths of the balanced schedule) against an fp32 product on the device
+    full = (aq.view(torch.float8_e4m3fn).float() @ wq.view(torch.float8_e4m3fn).float().T) * sa * sw.T
+    _check(C, full.cpu().numpy(), "decode all columns vs device fp32")
+
+
+@pytest.mark.parametrize("shape", [(1, 48, 128), (7, 2000, 256), (16, 10064, 256), (33, 17600, 128), (64, 9488, 384),
+                                   (8, 1032, 256), (64, 16, 1024), (16, 37888, 128), (8, 40000, 128), (24, 30000, 256)])
+def test_gemm_per_token_skinny_tile_widths(hk, shape):
+    """M <= 64: columns are dealt out in 16-column units as tiles of unequal width (1 to 16 units,
+    one tile per SM and round); these sizes hit narrow and wide tiles, every box size, a
+    single-unit problem, two rounds, and N % 16 != 0 (fixed-width fallback)."""
+    M, N, K = shape
+    aq, bq, sa, sb = _fp8_operands(M, N, K, seed=7)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(_dev(aq), _dev(bq), C, _dev(sa), _dev(sb))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C, gemm.gemm_fp8_per_token(aq, bq, sa, sb), f"skinny {shape}")
+
+
+def test_gemm_per_token_skinny_with_bias(hk):
+    M, N, K = 16, 2000, 256
+    aq, bq, sa, sb = _fp8_operands(M, N, K, seed=9)
+    bias = torch.randn(1, N, generator=torch.Generator().manual_seed(5)).bfloat16()
+    C = torch.full((1, M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.a8w8.dispatch(_dev(aq).view(1, M, K), _dev(bq).view(1, N, K), _dev(sa).view(1, M), _dev(sb).view(1, N), C,
+                                  _dev(bias))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C[0], gemm.gemm_fp8_per_token(aq, bq, sa, sb, bias.float().numpy()[0]), "skinny bias")
 
 
 # ---- block scales ---------------------------------------------------------------------------------
