@@ -35,6 +35,8 @@ SHIMS = {
     "gemm_afp4wfp4_tk": "HKB_SHIM_GEMM_AFP4WFP4",
     "batched_gemm_a8w8_tk": "HKB_SHIM_BATCHED_GEMM_A8W8",
     "batched_gemm_afp4wfp4_tk": "HKB_SHIM_BATCHED_GEMM_AFP4WFP4",
+    "fused_gemm_a8w8_blockscale_mul_add_tk": "HKB_SHIM_FUSED_GEMM_A8W8_BLOCKSCALE_MUL_ADD",
+    "fused_gemm_afp4wfp4_mul_add_tk": "HKB_SHIM_FUSED_GEMM_AFP4WFP4_MUL_ADD",
 }
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -79,6 +79,8 @@ struct GemmParams {
     const __nv_bfloat16* bias; // pts only: [batch, N] or null
     __nv_bfloat16* C;          // [batch, M, N]
     int gn;                    // blockscale: 1 or 128
+    const __nv_bfloat16* c_a;  // blockscale only: fused epilogue C = c_a * gemm + c_b, both [M, N]; null = plain
+    const __nv_bfloat16* c_b;
     uint32_t* status;
 };
 
@@ -128,6 +130,20 @@ __device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const float* v
                    "r"(pack_bf16(v[6], v[7])), "r"(pack_bf16(v[8], v[9])), "r"(pack_bf16(v[10], v[11])),
                    "r"(pack_bf16(v[12], v[13])), "r"(pack_bf16(v[14], v[15])) : "memory");
 }
+// v[0..NV) (consecutive columns of one row, starting at element offset `off` of the [M,N] arrays)
+// -> c_a * v + c_b in fp32: the fused multiply-add epilogue.
+template <int NV>
+__device__ __forceinline__ void mul_add_cols(const __nv_bfloat16* c_a, const __nv_bfloat16* c_b, int64_t off, float* v) {
+#pragma unroll
+    for (int j = 0; j < NV; j += 8) {
+        float ca[8], cb[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(c_a + off + j)), ca);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(c_b + off + j)), cb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j + i] = __fmaf_rn(ca[i], v[j + i], cb[i]);
+    }
+}
+
 // Writes 32 consecutive columns of one output row.  `wide` = rows are 32-byte aligned (N % 16 == 0);
 // otherwise 16-byte stores (N % 8 == 0 is guaranteed).
 __device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N, const float* v, bool wide) {
@@ -297,7 +313,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int acc = 0;
         uint32_t acc_ph = 0;
         bool ok = true;
-        const bool wide = (p.N % 16) == 0;
+        const bool wide = (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 31) == 0;
         for (int t = tile0; t < total_tiles && ok; t += tile_step) {
             const int b = t / tiles_per_batch;
             int mb, nb;
@@ -405,6 +421,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         float v[16];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) { v[2 * i] = acc2[c / 2 + i].x; v[2 * i + 1] = acc2[c / 2 + i].y; }
+                        if (p.c_a) mul_add_cols<16>(p.c_a, p.c_b, (int64_t)row * p.N + col_base + c, v);
                         store_bf16x16(crow + col_base + c, v);
                     }
                 }
@@ -442,7 +459,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 if (ok && row_ok) {
 #pragma unroll
-                    for (int c = 0; c < COLS_PER_GROUP; c += 32) store_row32(crow, col_base + c, p.N, accv + c, wide);
+                    for (int c = 0; c < COLS_PER_GROUP; c += 32) {
+                        if (p.c_a) mul_add_cols<32>(p.c_a, p.c_b, (int64_t)row * p.N + col_base + c, accv + c);
+                        store_row32(crow, col_base + c, p.N, accv + c, wide);
+                    }
                 }
             }
         }
@@ -530,6 +550,9 @@ int common_checks(const char* who, const void* A, const void* B, const void* C, 
 }
 
 }  // namespace
+
+int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
+                             const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream);
 }  // namespace hkb
 
 extern "C" {
@@ -585,15 +608,33 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
 
 int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                             int64_t M, int64_t N, int64_t K, void* stream) {
+    return hkb::gemm_fp8_blockscale_impl(A, B, C, sa, sb, gn, nullptr, nullptr, M, N, K, stream);
+}
+
+int hkb_gemm_fp8_blockscale_mul_add(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
+                                    const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream) {
     using namespace hkb;
+    HKB_REQUIRE(c_a && c_b, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale_mul_add: null c_a / c_b");
+    HKB_REQUIRE(aligned16(c_a) && aligned16(c_b), HKB_ERR_BAD_ALIGN, "gemm_fp8_blockscale_mul_add: c_a and c_b must be 16-byte aligned");
+    return gemm_fp8_blockscale_impl(A, B, C, sa, sb, gn, c_a, c_b, M, N, K, stream);
+}
+
+}  // extern "C"
+
+namespace hkb {
+
+int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
+                             const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream) {
     int rc = common_checks("gemm_fp8_blockscale", A, B, C, 1, M, N, K);
     if (rc != HKB_OK) return rc;
+    HKB_REQUIRE(gn != 128 || aligned32(C), HKB_ERR_BAD_ALIGN, "gemm_fp8_blockscale: C must be 32-byte aligned");
     HKB_REQUIRE(sa && sb, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale: null scale pointer");
     HKB_REQUIRE(gn == 1 || gn == 128, HKB_ERR_UNSUPPORTED, "gemm_fp8_blockscale: weight scale group along N must be 1 or 128, got %lld", (long long)gn);
     HKB_REQUIRE(N % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_fp8_blockscale: N=%lld must be a multiple of 128", (long long)N);
     GemmParams p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
     p.sa = sa; p.sb = sb; p.bias = nullptr; p.C = (__nv_bfloat16*)C; p.gn = (int)gn;
+    p.c_a = (const __nv_bfloat16*)c_a; p.c_b = (const __nv_bfloat16*)c_b;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
     p.m_blks = (int)((M + BM - 1) / BM);
@@ -625,4 +666,4 @@ int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* 
     return launch_gemm<128, 6, true, false>(tmA, tmB, p, st);
 }
 
-}  // extern "C"
+}  // namespace hkb

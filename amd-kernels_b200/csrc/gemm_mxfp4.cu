@@ -32,6 +32,8 @@ struct Mxfp4Params {
     const uint8_t* sfa;           // re-laid-out scales of A: [batch, m_blks, katoms, 512]
     const uint8_t* sfb;           // re-laid-out scales of B: [batch, sfb_rblks, katoms, 512]
     __nv_bfloat16* C;
+    const __nv_bfloat16* c_a;     // fused multiply-add epilogue C = c_a * (A B^T) + c_b, both [batch, M, N]; null = plain
+    const __nv_bfloat16* c_b;
     uint32_t* status;
 };
 
@@ -227,7 +229,8 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
             const int row = mb * BM + row_in_tile;
             const bool row_ok = row < p.M;
-            __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
+            const int64_t row_off = ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
+            __nv_bfloat16* crow = p.C + row_off;
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) break;
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_addr + acc * BN;
@@ -241,6 +244,13 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
                         if (col0 + j < p.N) {
+                            if (p.c_a) {
+                                float ca[8], cb[8];
+                                unpack8(__ldg(reinterpret_cast<const uint4*>(p.c_a + row_off + col0 + j)), ca);
+                                unpack8(__ldg(reinterpret_cast<const uint4*>(p.c_b + row_off + col0 + j)), cb);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) r[j + i] = __float_as_uint(__fmaf_rn(ca[i], __uint_as_float(r[j + i]), cb[i]));
+                            }
                             uint4 o;
                             __nv_bfloat162 q0 = __floats2bfloat162_rn(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
                             __nv_bfloat162 q1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
@@ -274,12 +284,8 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
 }
 
-}  // namespace
-}  // namespace hkb
-
-extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
-                              int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
-    using namespace hkb;
+int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, const void* sfb, const void* c_a, const void* c_b,
+                    int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
     HKB_REQUIRE(A && B && C && sfa && sfb, HKB_ERR_BAD_ARG, "gemm_mxfp4: null pointer");
     HKB_REQUIRE(batch >= 1 && M >= 1 && N >= 1 && K >= 1, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: empty problem");
     HKB_REQUIRE(K % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: K=%lld must be a multiple of 128", (long long)K);
@@ -302,6 +308,8 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
     const int katoms_src = (int)(K / 128);
     p.katoms = (katoms_src + 1) & ~1;
     p.C = (__nv_bfloat16*)C;
+    p.c_a = (const __nv_bfloat16*)c_a;
+    p.c_b = (const __nv_bfloat16*)c_b;
     int rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
 
@@ -341,6 +349,22 @@ extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void*
         gemm_mxfp4_kernel<128><<<grid, 192, Cfg<128>::kDynamic, st>>>(tmA, tmB, p);
     }
     return check_launch("gemm_mxfp4_kernel");
+}
+
+}  // namespace
+}  // namespace hkb
+
+extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                              int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+    return hkb::gemm_mxfp4_impl(A, B, C, sfa, sfb, nullptr, nullptr, batch, M, N, K, stream);
+}
+
+extern "C" int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                                      const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(c_a && c_b, HKB_ERR_BAD_ARG, "gemm_mxfp4_mul_add: null c_a / c_b");
+    HKB_REQUIRE(aligned16(c_a) && aligned16(c_b), HKB_ERR_BAD_ALIGN, "gemm_mxfp4_mul_add: c_a and c_b must be 16-byte aligned");
+    return gemm_mxfp4_impl(A, B, C, sfa, sfb, c_a, c_b, 1, M, N, K, stream);
 }
 
 

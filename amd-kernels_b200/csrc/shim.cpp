@@ -250,8 +250,9 @@ void fp8_pts(py::object A_, py::object B_, py::object C_, py::object sa_, py::ob
 // gemm_a8w8_blockscale_tk.dispatch(A, B, C, a_scale, b_scale):
 // kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:174-180.
 // a_scale [M, K/128]; b_scale [K/128, N/gn], gn = N / b_scale.shape[1] in {1, 128}.
-[[maybe_unused]] void dispatch_blockscale(py::object A_, py::object B_, py::object C_, py::object sa_, py::object sb_) {
-    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale");
+void blockscale(py::object A_, py::object B_, py::object C_, py::object sa_, py::object sb_, py::object ca_, py::object cb_) {
+    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale"),
+          ca = view(ca_, "c_a", true), cb = view(cb_, "c_b", true);
     want_dtype(A, "A", {"float8_e4m3fn", "uint8"});
     want_dtype(B, "B", {"float8_e4m3fn", "uint8"});
     want_dtype(C, "C", {"bfloat16"});
@@ -267,16 +268,36 @@ void fp8_pts(py::object A_, py::object B_, py::object C_, py::object sa_, py::ob
     if (ncols == 0 || d.N % ncols) fail("b_scale must be [K/128, N/gn]");
     const int64_t gn = d.N / ncols;
     if (gn != 1 && gn != 128) fail("b_scale group size along N must be 1 or 128, got " + std::to_string(gn));
-    same_device({&A, &B, &C, &sa, &sb});
+    if (ca.none != cb.none) fail("c_a and c_b go together");
+    if (!ca.none) {
+        want_dtype(ca, "c_a", {"bfloat16"});
+        want_dtype(cb, "c_b", {"bfloat16"});
+        if (ca.numel != d.M * d.N || cb.numel != d.M * d.N) fail("c_a and c_b must be [M, N]");
+    }
+    same_device({&A, &B, &C, &sa, &sb, &ca, &cb});
     Launch L(A.device);
-    check(hkb_gemm_fp8_blockscale(A.ptr, B.ptr, C.ptr, (const float*)sa.ptr, (const float*)sb.ptr, gn, d.M, d.N, d.K, L.stream));
+    if (ca.none)
+        check(hkb_gemm_fp8_blockscale(A.ptr, B.ptr, C.ptr, (const float*)sa.ptr, (const float*)sb.ptr, gn, d.M, d.N, d.K, L.stream));
+    else
+        check(hkb_gemm_fp8_blockscale_mul_add(A.ptr, B.ptr, C.ptr, (const float*)sa.ptr, (const float*)sb.ptr, gn, ca.ptr, cb.ptr,
+                                              d.M, d.N, d.K, L.stream));
+}
+[[maybe_unused]] void dispatch_blockscale(py::object A, py::object B, py::object C, py::object sa, py::object sb) {
+    blockscale(A, B, C, sa, sb, py::none(), py::none());
+}
+// fused_gemm_a8w8_blockscale_mul_add_tk.dispatch(a, b, c, a_scale, b_scale, c_a, c_b):
+// kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/kernel.cpp:184-193.  C = c_a * gemm + c_b.
+[[maybe_unused]] void dispatch_blockscale_mul_add(py::object A, py::object B, py::object C, py::object sa, py::object sb,
+                                                  py::object ca, py::object cb) {
+    if (ca.is_none() || cb.is_none()) fail("c_a and c_b are required");
+    blockscale(A, B, C, sa, sb, ca, cb);
 }
 
 // gemm_afp4wfp4_tk.dispatch(A, B, C[, a_scales, b_scales]) and the batched twin:
 // kernels/gemm-basic/gemm_afp4wfp4/kernel.cpp:154-158, kernels/gemm-batched/batched_gemm_afp4wfp4/kernel.cpp:164-167.
 // Operands are the packed form the reference's header comments specify (u8 [.., K/2] codes +
 // e8m0 [.., K/32] scales); the 3-argument bf16 "host-dequantized" form is a bf16 GEMM and is rejected.
-[[maybe_unused]] void dispatch_mxfp4(py::object A_, py::object B_, py::object C_, py::object sfa_, py::object sfb_) {
+void mxfp4(py::object A_, py::object B_, py::object C_, py::object sfa_, py::object sfb_, py::object ca_, py::object cb_) {
     if (sfa_.is_none() || sfb_.is_none())
         fail("gemm_afp4wfp4: pass packed e2m1 codes plus a_scales and b_scales (e8m0); "
              "the host-dequantized bf16 form is not supported");
@@ -289,9 +310,30 @@ void fp8_pts(py::object A_, py::object B_, py::object C_, py::object sa_, py::ob
     GemmDims d = gemm_dims(A, B, C, 2, 1);
     if (sfa.numel != d.batch * d.M * (d.K / 32)) fail("a_scales must be [batch, M, K/32]");
     if (sfb.numel != d.batch * d.N * (d.K / 32)) fail("b_scales must be [batch, N, K/32]");
-    same_device({&A, &B, &C, &sfa, &sfb});
+    TView ca = view(ca_, "c_a", true), cb = view(cb_, "c_b", true);
+    if (ca.none != cb.none) fail("c_a and c_b go together");
+    if (!ca.none) {
+        want_dtype(ca, "c_a", {"bfloat16"});
+        want_dtype(cb, "c_b", {"bfloat16"});
+        if (d.batch != 1) fail("the multiply-add form takes 2-D operands");
+        if (ca.numel != d.M * d.N || cb.numel != d.M * d.N) fail("c_a and c_b must be [M, N]");
+    }
+    same_device({&A, &B, &C, &sfa, &sfb, &ca, &cb});
     Launch L(A.device);
-    check(hkb_gemm_mxfp4(A.ptr, B.ptr, C.ptr, sfa.ptr, sfb.ptr, d.batch, d.M, d.N, d.K, L.stream));
+    if (ca.none)
+        check(hkb_gemm_mxfp4(A.ptr, B.ptr, C.ptr, sfa.ptr, sfb.ptr, d.batch, d.M, d.N, d.K, L.stream));
+    else
+        check(hkb_gemm_mxfp4_mul_add(A.ptr, B.ptr, C.ptr, sfa.ptr, sfb.ptr, ca.ptr, cb.ptr, d.M, d.N, d.K, L.stream));
+}
+[[maybe_unused]] void dispatch_mxfp4(py::object A, py::object B, py::object C, py::object sfa, py::object sfb) {
+    mxfp4(A, B, C, sfa, sfb, py::none(), py::none());
+}
+// fused_gemm_afp4wfp4_mul_add_tk.dispatch(a, b, c, a_scale, b_scale, c_a, c_b):
+// kernels/gemm-fused/fused_gemm_afp4wfp4_mul_add/kernel.cpp:182-191.  Packed e2m1 / e8m0 operands.
+[[maybe_unused]] void dispatch_mxfp4_mul_add(py::object A, py::object B, py::object C, py::object sfa, py::object sfb,
+                                             py::object ca, py::object cb) {
+    if (ca.is_none() || cb.is_none()) fail("c_a and c_b are required");
+    mxfp4(A, B, C, sfa, sfb, ca, cb);
 }
 
 }  // namespace
@@ -331,6 +373,12 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_BATCHED_GEMM_AFP4WFP4)
     m.doc() = "batched MXFP4 x MXFP4 GEMM, sm_100a tcgen05 block-scaled MMA";
     m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());
+#elif defined(HKB_SHIM_FUSED_GEMM_A8W8_BLOCKSCALE_MUL_ADD)
+    m.doc() = "block-scale FP8 GEMM with fused multiply-add epilogue C = c_a * gemm + c_b, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_blockscale_mul_add, "a"_a, "b"_a, "c"_a, "a_scale"_a, "b_scale"_a, "c_a"_a, "c_b"_a);
+#elif defined(HKB_SHIM_FUSED_GEMM_AFP4WFP4_MUL_ADD)
+    m.doc() = "MXFP4 x MXFP4 GEMM with fused multiply-add epilogue C = c_a * gemm + c_b, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_mxfp4_mul_add, "a"_a, "b"_a, "c"_a, "a_scale"_a, "b_scale"_a, "c_a"_a, "c_b"_a);
 #else
 #error "unknown shim selector"
 #endif

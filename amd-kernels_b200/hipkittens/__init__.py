@@ -172,7 +172,17 @@ class _BatchedGemmNamespace:
     a16wfp4 = _SubModule("batched_gemm_a16wfp4_tk")
 
 
+class _FusedGemmNamespace:
+    # quantized GEMM + multiply-add epilogue (C = c_a * gemm + c_b)
+    a8w8_blockscale_mul_add = _SubModule("fused_gemm_a8w8_blockscale_mul_add_tk")
+    afp4wfp4_mul_add = _SubModule("fused_gemm_afp4wfp4_mul_add_tk")
+    # names kept for compatibility; not built here (each pairs the quantized GEMM with a bf16 GEMM)
+    a8w8_blockscale_a16w16 = _SubModule("fused_gemm_a8w8_blockscale_a16w16_tk")
+    afp4wfp4_a16w16 = _SubModule("fused_gemm_afp4wfp4_a16w16_tk")
+
+
 gemm = _GemmNamespace()
 batched_gemm = _BatchedGemmNamespace()
+fused_gemm = _FusedGemmNamespace()
 
 from . import sharded  # noqa: E402,F401  (N-sharded block-scale GEMM over torch.distributed)

@@ -101,6 +101,15 @@ int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* 
                             const float* sb, int64_t gn, int64_t M, int64_t N, int64_t K,
                             void* stream);
 
+/* The same GEMM with the multiply-add epilogue fused in: C = bf16( c_a * gemm + c_b ), c_a and
+ * c_b bf16 [M, N] (16-byte aligned), evaluated in fp32 before the one rounding to bf16.  Replaces
+ * fused_gemm_a8w8_blockscale_mul_add_tk.dispatch(a,b,c,a_scale,b_scale,c_a,c_b):
+ *   kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/kernel.cpp:154-193
+ * (the reference's b_scale there is [K/128, N], i.e. gn = 1; gn = 128 is accepted as well). */
+int hkb_gemm_fp8_blockscale_mul_add(const void* A, const void* B, void* C, const float* sa,
+                                    const float* sb, int64_t gn, const void* c_a, const void* c_b,
+                                    int64_t M, int64_t N, int64_t K, void* stream);
+
 /* C[b] = bf16( dq(A[b]) @ dq(B[b])^T ), dq(v)[i,k] = e2m1(v[i,k]) * 2^(s[i,k/32]-127).
  * A u8 [batch, M, K/2], B u8 [batch, N, K/2], sfa u8 [batch, M, K/32], sfb u8 [batch, N, K/32].
  * K % 128 == 0, N % 8 == 0.  Uses library-owned scratch for the scale re-layout.  Replaces
@@ -110,6 +119,16 @@ int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* 
  * host-dequantized bf16). */
 int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                    int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* hkb_gemm_mxfp4 (batch 1) with the multiply-add epilogue fused in: C = bf16( c_a * gemm + c_b ),
+ * c_a and c_b bf16 [M, N] (16-byte aligned).  Replaces
+ * fused_gemm_afp4wfp4_mul_add_tk.dispatch(a,b,c,a_scale,b_scale,c_a,c_b):
+ *   kernels/gemm-fused/fused_gemm_afp4wfp4_mul_add/kernel.cpp:31-39,182-191
+ * (packed e2m1 + e8m0 operands as for hkb_gemm_mxfp4; the reference kernel takes host-dequantized
+ * bf16 and fp32 scales per 32). */
+int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
+                           const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K,
+                           void* stream);
 
 /* hkb_gemm_mxfp4 for callers that must not allocate device memory at call time (arena / pool
  * disciplines that account for every byte up front, serving loops that cannot take cudaMalloc's

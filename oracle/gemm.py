@@ -90,6 +90,31 @@ def gemm_mxfp4(Aq, Bq, sfa, sfb):
     return (A @ B.transpose(-1, -2)).numpy()
 
 
+def gemm_group32_f32(A, B, sa, sb, group=32):
+    """C = sum_kb (A_kb @ B_kb^T) * sa[:, kb, None] * sb[:, kb][None, :] on decoded operand values
+    with fp32 scales per `group` K elements for both operands, sa [M, K/group], sb [N, K/group]
+    (kernels/gemm-fused/fused_gemm_afp4wfp4_mul_add/test_parity.py:22-37; tests/test_gemm.py:601-606).
+    With power-of-two scales this equals gemm_mxfp4 on the same codes."""
+    A = _t(_f32(A))
+    B = _t(_f32(B))
+    sa = _t(_f32(sa))
+    sb = _t(_f32(sb))
+    M, K = A.shape
+    N = B.shape[0]
+    C = torch.zeros(M, N, dtype=torch.float32)
+    for kb in range(K // group):
+        ks = slice(kb * group, (kb + 1) * group)
+        C += (A[:, ks] @ B[:, ks].T) * sa[:, kb, None] * sb[:, kb][None, :]
+    return C.numpy()
+
+
+def mul_add(G, c_a, c_b):
+    """Fused epilogue of the *_mul_add GEMMs: c_a.float() * gemm_out + c_b.float(), in fp32, the
+    GEMM result not yet rounded (tests/test_gemm.py:527 and :608;
+    kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/test_parity.py:36-38)."""
+    return (_f32(c_a) * _f32(G) + _f32(c_b)).astype(np.float32)
+
+
 def rel_err(C, C_ref):
     """max |C - C_ref| / (max |C_ref| + 1e-8), both fp32 (tests/test_gemm.py:190-192)."""
     C = _f32(C).astype(np.float64)

@@ -14,6 +14,11 @@ Fixtures (all seed 42, the reference tests' seed):
       re-expressed as packed e2m1 codes + e8m0 scale bytes that dequantize to exactly its operands
   quant_int8_per_token.npz   the expression of tests/test_misc.py:531-536 on its 1024x4096 input (first 64 rows)
   quant_static_fp8.npz       the expression of tests/test_moe.py:984-999 (256x128, scale 0.5)
+  fused_blockscale_mul_add.npz   reference_blockscale_gemm_mul_add on generate_test_data()
+      kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/test_parity.py:20-50 (output only; the inputs are
+      np.random.seed(42) draws that the test regenerates, checked through a_sum / c_b_sum)
+  fused_afp4_mul_add.npz         reference_fp4_gemm_mul_add on generate_test_data()
+      kernels/gemm-fused/fused_gemm_afp4wfp4_mul_add/test_parity.py:22-51 (same form)
   e2m1_lut.npz               FP4_LUT / decode_mx_scale of kernels/moe-gemm/moe_op_mxfp4/test_parity.py:30-46
 """
 import argparse
@@ -54,6 +59,17 @@ def main():
         A, B, sa, sb, C = bs.reference_gemm_a8w8_blockscale(M, N, K, group_k=128, group_n=gn)
         np.savez_compressed(os.path.join(HERE, f"gemm_blockscale_{M}x{N}x{K}_gn{gn}.npz"),
                             A=A.numpy(), B=B.numpy(), a_scale=sa.numpy(), b_scale=sb.numpy(), C_bf16=_bf16_bits(C))
+
+    ma = _load(os.path.join(k, "gemm-fused/fused_gemm_a8w8_blockscale_mul_add/test_parity.py"), "ref_bs_ma")
+    a, b, sa, sb, c_a, c_b = ma.generate_test_data()
+    ref = ma.reference_blockscale_gemm_mul_add(a, b, sa, sb, c_a, c_b, ma.GROUP_K)
+    np.savez_compressed(os.path.join(HERE, "fused_blockscale_mul_add.npz"), ref=ref.astype(np.float32),
+                        a_sum=np.float64(a.astype(np.float64).sum()), c_b_sum=np.float64(c_b.astype(np.float64).sum()))
+    fa = _load(os.path.join(k, "gemm-fused/fused_gemm_afp4wfp4_mul_add/test_parity.py"), "ref_fp4_ma")
+    a, b, sa, sb, c_a, c_b = fa.generate_test_data()
+    ref = fa.reference_fp4_gemm_mul_add(a, b, sa, sb, c_a, c_b, fa.SCALE_GROUP)
+    np.savez_compressed(os.path.join(HERE, "fused_afp4_mul_add.npz"), ref=ref.astype(np.float32),
+                        a_sum=np.float64(a.astype(np.float64).sum()), c_b_sum=np.float64(c_b.astype(np.float64).sum()))
 
     fb = _load(os.path.join(k, "gemm-batched/batched_gemm_afp4wfp4/test_parity.py"), "ref_fp4b")
     A_dq, B_dq, C = fb.reference_torch()          # A [B,M,K] bf16, B [B,K,N] bf16, C [B,M,N] bf16

@@ -94,7 +94,8 @@ def test_compute_without_a_gpu_fails_loudly_instead_of_falling_back(lib):
 # ---- the Python loader ----------------------------------------------------------------------------
 
 HOT_MODULES = ["quant_tk", "fused_fp8_quant_tk", "fused_mxfp4_quant_tk", "gemm_a8w8_tk", "gemm_a8w8_per_token_scale_tk",
-               "gemm_a8w8_blockscale_tk", "gemm_afp4wfp4_tk", "batched_gemm_a8w8_tk", "batched_gemm_afp4wfp4_tk"]
+               "gemm_a8w8_blockscale_tk", "gemm_afp4wfp4_tk", "batched_gemm_a8w8_tk", "batched_gemm_afp4wfp4_tk",
+               "fused_gemm_a8w8_blockscale_mul_add_tk", "fused_gemm_afp4wfp4_mul_add_tk"]
 
 
 def test_loader_discovers_the_reference_module_names(hk):
@@ -115,6 +116,9 @@ def test_functions_and_argument_names_match_the_reference_bindings(hk):
     assert d.startswith("dispatch(A: object, B: object, C: object, a_scale: object, b_scale: object)")
     d = hk.batched_gemm.a8w8.dispatch.__doc__
     assert d.startswith("dispatch(A: object, B: object, a_scale: object, b_scale: object, C: object, bias: object")
+    for mod in (hk.fused_gemm.a8w8_blockscale_mul_add, hk.fused_gemm.afp4wfp4_mul_add):
+        assert mod.dispatch.__doc__.startswith(
+            "dispatch(a: object, b: object, c: object, a_scale: object, b_scale: object, c_a: object, c_b: object)")
     d = hk.modules["fused_fp8_quant_tk"].fused_rmsnorm_fp8_quant_fwd.__doc__
     assert d.startswith("fused_rmsnorm_fp8_quant_fwd(input: object, weight: object, output: object, scales: object, eps: ")
     d = hk.modules["fused_mxfp4_quant_tk"].fused_rmsnorm_mxfp4_quant_fwd.__doc__
@@ -124,6 +128,8 @@ def test_functions_and_argument_names_match_the_reference_bindings(hk):
 def test_modules_off_the_path_raise_the_reference_error(hk):
     with pytest.raises(RuntimeError, match="Kernel module 'gemm_a16w16_tk' not found. Did you compile it?"):
         hk.gemm.a16w16.dispatch(None, None, None)
+    with pytest.raises(RuntimeError, match="Kernel module 'fused_gemm_afp4wfp4_a16w16_tk' not found"):
+        hk.fused_gemm.afp4wfp4_a16w16.dispatch(None)
     with pytest.raises(RuntimeError, match="not found"):
         hk.modules["rmsnorm_tk"]
 

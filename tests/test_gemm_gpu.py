@@ -330,3 +330,60 @@ def test_config3_quantize_then_mxfp4_gemm_sampled(hk):
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(2))[:128].sort().values.to(DEV)
     ref = gemm.gemm_mxfp4(ac[rows].cpu(), wc.cpu(), asc[rows].cpu(), wsc.cpu())
     _check(C[rows], ref, "config 3 (M=2048) sampled rows")
+
+
+# ---- fused multiply-add epilogue (C = c_a * gemm + c_b) ---------------------------------------------
+
+def _ca_cb(M, N, seed=11):
+    """c_a, c_b ~ N(0, 0.5) bf16 [M, N], as in the reference's tests (tests/test_gemm.py:516-517)."""
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(M, N, generator=g) * 0.5).bfloat16(), (torch.randn(M, N, generator=g) * 0.5).bfloat16()
+
+
+@pytest.mark.parametrize("shape,gn", [((256, 256, 256), 1),            # the reference's case: b_scale [K/128, N]
+                                      ((256, 256, 256), 128), ((512, 1024, 512), 128),
+                                      ((200, 384, 256), 128), ((2304, 4608, 256), 128)])   # 256-wide tiles
+def test_fused_blockscale_mul_add(hk, shape, gn):
+    """fused_gemm_a8w8_blockscale_mul_add (reference test: tests/test_gemm.py:498-533): scales
+    rand*2.0 as there, operands e4m3-representable."""
+    M, N, K = shape
+    aq, bq, _, _ = _fp8_operands(M, N, K)
+    g = torch.Generator().manual_seed(7)
+    sa = torch.rand(M, K // 128, generator=g) * 2.0
+    sb = torch.rand(K // 128, N // gn, generator=g) * 2.0
+    c_a, c_b = _ca_cb(M, N)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.fused_gemm.a8w8_blockscale_mul_add.dispatch(_dev(aq), _dev(bq), C, _dev(sa), _dev(sb), _dev(c_a), _dev(c_b))
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = gemm.mul_add(gemm.gemm_fp8_blockscale(aq, bq, sa, sb), c_a, c_b)
+    _check(C, ref, f"blockscale mul_add {shape} gn={gn}")
+    # and the epilogue really is applied to the unrounded GEMM of the plain entry point
+    P = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(_dev(aq), _dev(bq), P, _dev(sa), _dev(sb))
+    two_step = (c_a.float() * P.float().cpu() + c_b.float()).numpy()
+    assert gemm.rel_err(C.float().cpu().numpy(), two_step) < 2 ** -7
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (200, 264, 512), (2304, 3264, 256)])
+def test_fused_mxfp4_mul_add(hk, shape):
+    """fused_gemm_afp4wfp4_mul_add (reference test: tests/test_gemm.py:579-614) on packed e2m1 codes
+    and e8m0 scales."""
+    M, N, K = shape
+    ac, wc, asc, wsc = _mxfp4_operands(M, N, K)
+    c_a, c_b = _ca_cb(M, N)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.fused_gemm.afp4wfp4_mul_add.dispatch(_dev(ac), _dev(wc), C, _dev(asc), _dev(wsc), _dev(c_a), _dev(c_b))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C, gemm.mul_add(gemm.gemm_mxfp4(ac, wc, asc, wsc), c_a, c_b), f"mxfp4 mul_add {shape}")
+
+
+def test_fused_mul_add_validates_its_operands(hk):
+    x8 = torch.zeros(128, 128, dtype=torch.uint8, device=DEV)
+    c = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    s = torch.ones(128, 1, device=DEV)
+    with pytest.raises(RuntimeError, match="c_a and c_b must be"):
+        hk.fused_gemm.a8w8_blockscale_mul_add.dispatch(x8, x8, c, s, s.view(1, 128), c[:64], c)
+    with pytest.raises(RuntimeError, match="c_a"):
+        hk.fused_gemm.a8w8_blockscale_mul_add.dispatch(x8, x8, c, s, s.view(1, 128), c.float(), c)

@@ -164,6 +164,45 @@ def test_gemm_mxfp4_batched_golden(golden_dir):
     assert gemm.rel_err(torch.from_numpy(C).bfloat16(), ref) < 2 ** -8
 
 
+def _fused_test_data(group):
+    """generate_test_data() of the reference's two *_mul_add parity scripts (M = N = K = 256,
+    np.random.seed(42)); b_scale is [K/128, N] for the block-scale form (group 128) and
+    [N, K/32] for the fp4 form (group 32)."""
+    np.random.seed(42)
+    M = N = K = 256
+    a = np.random.randn(M, K).astype(np.float32) * 0.1
+    b = np.random.randn(N, K).astype(np.float32) * 0.1
+    a_scale = np.random.rand(M, K // group).astype(np.float32) * 2.0
+    b_scale = (np.random.rand(K // group, N) if group == 128 else np.random.rand(N, K // group)).astype(np.float32) * 2.0
+    c_a = np.random.randn(M, N).astype(np.float32) * 0.5
+    c_b = np.random.randn(M, N).astype(np.float32) * 0.5
+    return a, b, a_scale, b_scale, c_a, c_b
+
+
+def test_fused_blockscale_mul_add_golden(golden_dir):
+    g = _load(golden_dir, "fused_blockscale_mul_add.npz")
+    a, b, sa, sb, c_a, c_b = _fused_test_data(128)
+    assert abs(a.astype(np.float64).sum() - float(g["a_sum"])) < 1e-9 and abs(c_b.astype(np.float64).sum() - float(g["c_b_sum"])) < 1e-9
+    out = gemm.mul_add(gemm.gemm_blockscale_f32(a, b, sa, sb), c_a, c_b)
+    assert gemm.rel_err(out, g["ref"]) < 1e-5
+
+
+def test_fused_afp4_mul_add_golden(golden_dir):
+    g = _load(golden_dir, "fused_afp4_mul_add.npz")
+    a, b, sa, sb, c_a, c_b = _fused_test_data(32)
+    assert abs(a.astype(np.float64).sum() - float(g["a_sum"])) < 1e-9 and abs(c_b.astype(np.float64).sum() - float(g["c_b_sum"])) < 1e-9
+    out = gemm.mul_add(gemm.gemm_group32_f32(a, b, sa, sb), c_a, c_b)
+    assert gemm.rel_err(out, g["ref"]) < 1e-5
+
+
+def test_group32_gemm_with_power_of_two_scales_is_the_mxfp4_gemm(golden_dir):
+    g = _load(golden_dir, "gemm_afp4_batched.npz")
+    from oracle.codecs import e8m0_to_f32, unpack_e2m1
+    A, B = unpack_e2m1(g["A"][0]), unpack_e2m1(g["B"][0])
+    C = gemm.gemm_group32_f32(A, B, e8m0_to_f32(g["a_scales"][0]), e8m0_to_f32(g["b_scales"][0]))
+    assert gemm.rel_err(C, gemm.gemm_mxfp4(g["A"][0], g["B"][0], g["a_scales"][0], g["b_scales"][0])) < 1e-6
+
+
 def test_fp8_gemm_oracle_is_dequantize_then_matmul():
     A, W = inputs.make_config("c1")
     aq, sa = quant.quant_fp8_per_token(A)
