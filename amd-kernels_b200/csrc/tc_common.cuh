@@ -72,14 +72,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // status word and the abort flag is set so that every role of the CTA winds down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t err_bit) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    // The clock is read only every 1024 polls, the first time after 1024 polls: a %globaltimer
+    // read costs hundreds of cycles, and a wait that is about to succeed must not sit behind one
+    // (roles that hand a buffer back and forth per K block wait on every hand-off).
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3FF) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
                 *abort_flag = 1;
                 atomicOr(status, err_bit);
                 return false;
