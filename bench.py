@@ -61,9 +61,9 @@ L2_FLUSH_BYTES = 256 << 20
 # (profiles/ has the captures); None = not captured.
 NCU_TRAFFIC = {
     "c2": 290.1e6,       # profiles/c2_gemm_fp8_blockscale.md
-    "c3": 191.7e6,       # profiles/c3_gemm_mxfp4.md
-    "c4a": 239.4e6,      # profiles/c4a_gemm_fp8_decode.md
-    "c4b": 166.3e6,      # profiles/c4b_gemm_fp8_per_token_pairs.md
+    "c3": 199.6e6,       # profiles/c3_gemm_mxfp4.md
+    "c4a": 241.4e6,      # profiles/c4a_gemm_fp8_decode.md
+    "c4b": 166.5e6,      # profiles/c4b_gemm_fp8_per_token_pairs.md
     "qbw-fp8": 373.3e6,  # profiles/qbw_quant_per_token_fp8.md
 }
 
@@ -353,7 +353,7 @@ class L2Flush:
 
     def __init__(self, dev):
         self.w = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
-        self.r = torch.zeros(L2_FLUSH_BYTES // 2, dtype=torch.int32, device=dev)
+        self.r = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int64, device=dev)   # 2 x the write buffer; int64 so that sum() needs no cast pass
         self.sink = torch.zeros((), dtype=torch.int64, device=dev)
 
     def __call__(self):
