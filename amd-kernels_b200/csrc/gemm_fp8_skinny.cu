@@ -24,8 +24,6 @@
 //
 // Roles, bounded waits and teardown as in gemm_fp8.cu: warp 0 TMA producer, warp 1 TMEM
 // allocator + MMA issuer, warps 2-5 epilogue (two TMEM accumulators of 256 columns).
-#include <cstdlib>
-
 #include "tc_common.cuh"
 
 namespace hkb {
@@ -223,6 +221,9 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
 }
 
+#undef TILE_WIDTH
+#undef TILE_COL0
+
 }  // namespace
 
 // Host side: called by hkb_gemm_fp8_pts for M <= 64, batch == 1, N % 16 == 0 (arguments already validated).
@@ -243,12 +244,11 @@ int launch_gemm_fp8_skinny(const void* A, const void* B, void* C, const float* s
     p.rem = units % p.tiles;
     const int maxw = p.base + (p.rem ? 1 : 0);
     HKB_REQUIRE(maxw >= 1 && maxw <= 16, HKB_ERR_UNSUPPORTED, "gemm_fp8 (skinny): internal tile width %d out of range", maxw);
-    static const int rot_env = [] { const char* v = getenv("HKB_SKINNY_ROT"); return v ? atoi(v) : -1; }();
     p.stage_bytes = p.a_bytes + maxw * 2048;
     p.stages = (kSmemLimit - 1024 - kBarBytes - kTailPad) / p.stage_bytes;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
     HKB_REQUIRE(p.stages >= 2, HKB_ERR_UNSUPPORTED, "gemm_fp8 (skinny): not enough shared memory for two stages");
-    p.rot = rot_env >= 0 ? rot_env : 17;
+    p.rot = 17;      // odd, so consecutive CTAs spread over all K blocks; measured best of {0, 1, 5, 17}
     const int smem = 1024 + kBarBytes + p.stages * p.stage_bytes + kTailPad;
     CUtensorMap tmA, tmB128, tmB64, tmB16;
     int rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)M, 1, (uint32_t)p.a_box_rows);
