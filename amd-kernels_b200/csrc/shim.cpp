@@ -336,6 +336,46 @@ void mxfp4(py::object A_, py::object B_, py::object C_, py::object sfa_, py::obj
     mxfp4(A, B, C, sfa, sfb, ca, cb);
 }
 
+// quant_moe_tk: kernels/moe-misc/quant_moe/kernel.cpp:392-476 (same names, argument order and the
+// redundant integer size arguments, which are checked against the tensors).
+[[maybe_unused]] void downcast_to_static_fp8(py::object x_, py::object y_, py::object scale_, int64_t M, int64_t N) {
+    TView x = view(x_, "x"), y = view(y_, "y"), sc = view(scale_, "scale");
+    want_dtype(x, "x", {"bfloat16"});
+    want_dtype(y, "y", {"float8_e4m3fn", "uint8"});
+    want_dtype(sc, "scale", {"float32"});
+    if (M < 0 || N < 0 || x.numel != M * N || y.numel != M * N) fail("x and y must have M*N elements");
+    if (sc.numel < 1) fail("scale must hold one float");
+    same_device({&x, &y, &sc});
+    Launch L(x.device);
+    check(hkb_moe_downcast_static_fp8(x.ptr, y.ptr, (const float*)sc.ptr, M, N, L.stream));
+}
+[[maybe_unused]] void downcast_to_mxfp(py::object t_, py::object s_, py::object src_, int64_t outer_dim, int64_t quant_dim, bool is_fp4) {
+    TView t = view(t_, "mx_tensor"), sc = view(s_, "mx_scale"), src = view(src_, "src");
+    want_dtype(src, "src", {"bfloat16"});
+    want_dtype(t, "mx_tensor", {"uint8", "float8_e4m3fn", "float4_e2m1fn_x2"});
+    want_dtype(sc, "mx_scale", {"uint8", "float8_e8m0fnu"});
+    if (quant_dim <= 0 || quant_dim % 32) fail("quant_dim must be a positive multiple of 32");
+    if (outer_dim < 0 || src.numel != outer_dim * quant_dim) fail("src must have outer_dim*quant_dim elements");
+    if (t.numel != outer_dim * quant_dim / (is_fp4 ? 2 : 1)) fail("mx_tensor must have outer_dim*quant_dim (FP8) or half as many (FP4) bytes");
+    if (sc.numel != outer_dim * (quant_dim / 32)) fail("mx_scale must have outer_dim*quant_dim/32 bytes");
+    same_device({&t, &sc, &src});
+    Launch L(src.device);
+    check(hkb_moe_downcast_mxfp(t.ptr, sc.ptr, src.ptr, outer_dim, quant_dim, is_fp4 ? 1 : 0, L.stream));
+}
+[[maybe_unused]] void upcast_from_mxfp(py::object out_, py::object s_, py::object t_, int64_t outer_dim, int64_t quant_dim, bool is_fp4) {
+    TView out = view(out_, "out"), sc = view(s_, "mx_scale"), t = view(t_, "mx_tensor");
+    want_dtype(out, "out", {"bfloat16"});
+    want_dtype(t, "mx_tensor", {"uint8", "float8_e4m3fn", "float4_e2m1fn_x2"});
+    want_dtype(sc, "mx_scale", {"uint8", "float8_e8m0fnu"});
+    if (quant_dim <= 0 || quant_dim % 32) fail("quant_dim must be a positive multiple of 32");
+    if (outer_dim < 0 || out.numel != outer_dim * quant_dim) fail("out must have outer_dim*quant_dim elements");
+    if (t.numel != outer_dim * quant_dim / (is_fp4 ? 2 : 1)) fail("mx_tensor must have outer_dim*quant_dim (FP8) or half as many (FP4) bytes");
+    if (sc.numel != outer_dim * (quant_dim / 32)) fail("mx_scale must have outer_dim*quant_dim/32 bytes");
+    same_device({&out, &sc, &t});
+    Launch L(out.device);
+    check(hkb_moe_upcast_mxfp(out.ptr, sc.ptr, t.ptr, outer_dim, quant_dim, is_fp4 ? 1 : 0, L.stream));
+}
+
 }  // namespace
 
 #ifndef HKB_SHIM_NAME
@@ -379,6 +419,11 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_FUSED_GEMM_AFP4WFP4_MUL_ADD)
     m.doc() = "MXFP4 x MXFP4 GEMM with fused multiply-add epilogue C = c_a * gemm + c_b, sm_100a tcgen05";
     m.def("dispatch", &dispatch_mxfp4_mul_add, "a"_a, "b"_a, "c"_a, "a_scale"_a, "b_scale"_a, "c_a"_a, "c_b"_a);
+#elif defined(HKB_SHIM_QUANT_MOE)
+    m.doc() = "MoE casts: static FP8 down-cast, MX (e4m3 / e2m1 + exponent byte per 32) down- and up-cast, sm_100a";
+    m.def("downcast_to_static_fp8", &downcast_to_static_fp8, "x"_a, "y"_a, "scale"_a, "M"_a, "N"_a);
+    m.def("downcast_to_mxfp", &downcast_to_mxfp, "mx_tensor"_a, "mx_scale"_a, "src"_a, "outer_dim"_a, "quant_dim"_a, "is_fp4"_a);
+    m.def("upcast_from_mxfp", &upcast_from_mxfp, "out"_a, "mx_scale"_a, "mx_tensor"_a, "outer_dim"_a, "quant_dim"_a, "is_fp4"_a);
 #else
 #error "unknown shim selector"
 #endif

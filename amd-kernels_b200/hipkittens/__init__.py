@@ -181,8 +181,20 @@ class _FusedGemmNamespace:
     afp4wfp4_a16w16 = _SubModule("fused_gemm_afp4wfp4_a16w16_tk")
 
 
+class _MoeRoutingNamespace:
+    # the MoE activation / weight casts (static FP8, MX FP8 / FP4 down- and up-cast)
+    quant = _SubModule("quant_moe_tk")
+    # names kept for compatibility; not built here (routing, not quantization)
+    align_block_size = _SubModule("moe_align_block_size_tk")
+    bitmatrix = _SubModule("moe_bitmatrix_tk")
+    expt_data = _SubModule("moe_expt_data_tk")
+    topk = _SubModule("moe_topk_tk")
+    sigmoid_top1_fused = _SubModule("moe_routing_sigmoid_top1_fused_tk")
+
+
 gemm = _GemmNamespace()
 batched_gemm = _BatchedGemmNamespace()
 fused_gemm = _FusedGemmNamespace()
+moe_routing = _MoeRoutingNamespace()
 
 from . import sharded  # noqa: E402,F401  (N-sharded block-scale GEMM over torch.distributed)

@@ -53,6 +53,11 @@ WORKLOADS = {
     "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
     "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),
     "qbw-mxfp4-16k": ("quant-mxfp4", 1, 16384, 0, 8192),
+    # quant_moe_tk casts (static FP8, MX FP8 / FP4 down-cast, MX FP8 up-cast)
+    "qbw-moe-static": ("quant-moe-static", 1, 16384, 0, 8192),
+    "qbw-moe-mxfp8": ("quant-moe-mxfp8", 1, 16384, 0, 8192),
+    "qbw-moe-mxfp4": ("quant-moe-mxfp4", 1, 16384, 0, 8192),
+    "qbw-moe-up8": ("quant-moe-up8", 1, 16384, 0, 8192),
 }
 METRIC = "quant GEMM TFLOPS & % of FP8/FP4 tensor peak; quantizer GB/s vs HBM peak"
 L2_FLUSH_BYTES = 256 << 20
@@ -147,6 +152,10 @@ def quant_bytes(kind, M, D):
         return M * D * 3 + M * 4
     if kind == "quant-1x128":
         return M * D * 3 + M * (D // 128) * 4
+    if kind == "quant-moe-static":
+        return M * D * 3
+    if kind in ("quant-moe-mxfp8", "quant-moe-up8"):
+        return M * D * 3 + M * D // 32
     return M * D * 2 + M * D // 2 + M * D // 32
 
 
@@ -174,9 +183,16 @@ class Workload:
         if self.kind.startswith("quant"):
             self.N = 0
             self.x = torch.randn(M, K, generator=g, device=dev, dtype=torch.float32).bfloat16()
-            if self.kind == "quant-mxfp4":
+            if self.kind in ("quant-mxfp4", "quant-moe-mxfp4"):
                 self.q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
                 self.s = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+            elif self.kind.startswith("quant-moe"):
+                self.q = torch.empty(M, K, dtype=torch.uint8, device=dev)
+                self.s = (torch.full((1,), 0.01, dtype=torch.float32, device=dev) if self.kind == "quant-moe-static"
+                          else torch.empty(M, K // 32, dtype=torch.uint8, device=dev))
+                if self.kind == "quant-moe-up8":          # codes to decode: the down-cast of x
+                    hk.moe_routing.quant.downcast_to_mxfp(self.q, self.s, self.x, M, K, False)
+                    self.up = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
             else:
                 self.q = torch.empty(M, K, dtype=torch.uint8, device=dev)
                 self.s = torch.empty(M, 1 if self.kind == "quant-fp8" else K // 128, dtype=torch.float32, device=dev)
@@ -238,6 +254,14 @@ class Workload:
             hk.per_token_quant_fwd(self.x, self.q, self.s)
         elif self.kind == "quant-1x128":
             hk.fused_rmsnorm_fp8_quant_fwd(self.x, None, self.q, self.s, 1e-6)
+        elif self.kind == "quant-moe-static":
+            hk.moe_routing.quant.downcast_to_static_fp8(self.x, self.q, self.s, self.M, K)
+        elif self.kind == "quant-moe-mxfp8":
+            hk.moe_routing.quant.downcast_to_mxfp(self.q, self.s, self.x, self.M, K, False)
+        elif self.kind == "quant-moe-mxfp4":
+            hk.moe_routing.quant.downcast_to_mxfp(self.q, self.s, self.x, self.M, K, True)
+        elif self.kind == "quant-moe-up8":
+            hk.moe_routing.quant.upcast_from_mxfp(self.up, self.s, self.q, self.M, K, False)
         else:
             hk.fused_rmsnorm_mxfp4_quant_fwd(self.x, None, self.q, self.s, 1e-6)
 
@@ -401,7 +425,7 @@ def cpu_reference_step(name, sample_rows):
     """One pass of the path on the CPU with the oracle (torch CPU + NumPy), on `sample_rows` rows
     of the activations and at most CPU_SAMPLE_MAX_N weight rows (all of K).
     Returns (seconds, units of work done, unit)."""
-    from oracle import gemm as ogemm, quant as oquant
+    from oracle import gemm as ogemm, quant as oquant, quant_moe as omoe
     kind, B, M, N, K = WORKLOADS[name]
     if N > CPU_SAMPLE_MAX_N:
         N = CPU_SAMPLE_MAX_N // 128 * 128
@@ -437,6 +461,15 @@ def cpu_reference_step(name, sample_rows):
         C = oquant.quant_fp8_per_token(A)
     elif kind == "quant-1x128":
         C = oquant.quant_fp8_1x128(A)
+    elif kind == "quant-moe-static":
+        C = omoe.downcast_to_static_fp8(A, 0.01)
+    elif kind in ("quant-moe-mxfp8", "quant-moe-mxfp4"):
+        C = omoe.downcast_to_mxfp(A, kind == "quant-moe-mxfp4")
+    elif kind == "quant-moe-up8":
+        if "codes" not in st:
+            st["codes"], st["sb"] = omoe.downcast_to_mxfp(A, False)
+            t0 = time.perf_counter()
+        C = omoe.upcast_from_mxfp(st["codes"], st["sb"], False)
     else:
         C = oquant.quant_mxfp4(A)
     if not kind.startswith("quant"):
@@ -565,7 +598,7 @@ def main():
 
     # end to end through the public API with host buffers
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and wl.kind != "quant-moe-up8":   # the up-cast takes codes, not activations: no host-buffer form here
         wl.setup_e2e()
         barrier(world)
         e_steps = max(4, min(args.steps, 20))

@@ -130,6 +130,30 @@ int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, const void* sf
                            const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K,
                            void* stream);
 
+/* quant_moe_tk: wire formats of the MoE activation/weight casts.  Replace
+ *   quant_moe_tk.downcast_to_static_fp8(x, y, scale, M, N)
+ *   quant_moe_tk.downcast_to_mxfp(mx_tensor, mx_scale, src, outer_dim, quant_dim, is_fp4)
+ *   quant_moe_tk.upcast_from_mxfp(out, mx_scale, mx_tensor, outer_dim, quant_dim, is_fp4)
+ *       kernels/moe-misc/quant_moe/kernel.cpp:74-107, 143-231, 289-359, 392-476
+ * x / src / out bf16 row-major; y and FP8 codes 1 byte per element (e4m3fn); FP4 codes e2m1, two per
+ * byte, element 2i in the low nibble; mx_scale one byte per 32 elements of the last dimension.
+ *  - static: y = e4m3fn(clamp(x / scale[0], +-448)), true division, round-to-nearest-even
+ *    (tests/test_moe.py:997-999; the reference device code truncates instead, :56-71).
+ *  - downcast: byte = biased exponent of amax / QMAX rounded up to a power of two (:155-158; QMAX 448,
+ *    or 6 for FP4), codes = x * 2^(127 - byte) rounded to nearest even, saturating.  An all-zero block
+ *    gets byte 127 (the reference's Python path, test_parity.py:116-117; its device code writes 255,
+ *    which its own up-cast turns into NaN).  The reference leaves the FP4 codes unwritten (:214-217);
+ *    here they follow the same rule with QMAX 6.
+ *  - upcast: out = bf16(decode(code) * float_from_bits(byte << 23)); byte 255 gives NaN (:313-321),
+ *    byte 0 gives 0.
+ * quant_dim % 32 == 0; src/out 32-byte, codes 16-byte, scales 4-byte aligned. */
+int hkb_moe_downcast_static_fp8(const void* x, void* y, const float* scale, int64_t M, int64_t N,
+                                void* stream);
+int hkb_moe_downcast_mxfp(void* mx_tensor, void* mx_scale, const void* src, int64_t outer_dim,
+                          int64_t quant_dim, int is_fp4, void* stream);
+int hkb_moe_upcast_mxfp(void* out, const void* mx_scale, const void* mx_tensor, int64_t outer_dim,
+                        int64_t quant_dim, int is_fp4, void* stream);
+
 /* hkb_gemm_mxfp4 for callers that must not allocate device memory at call time (arena / pool
  * disciplines that account for every byte up front, serving loops that cannot take cudaMalloc's
  * device-wide synchronisation, devices whose memory the host has already claimed in full).
