@@ -90,7 +90,10 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
     if constexpr (TPR > 32) {
         __shared__ float s_am[8];
         if ((tid & 31) == 0) s_am[tid >> 5] = am;
-        __syncthreads();
+        // only the warps of this row wait for one another (named barrier 1 + row-in-CTA): rows of
+        // one CTA stay independent, so a slow load of one row does not hold back the others
+        if constexpr (TPR == 256) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + r_in), "r"(TPR) : "memory");
         constexpr int WPR = TPR / 32;
         am = s_am[r_in * WPR];
 #pragma unroll
@@ -167,7 +170,7 @@ int quant_per_token(const void* x, void* q, float* scales, int64_t M, int64_t D,
     const bool wide_ok = D % 16 == 0 && ldx % 16 == 0 && aligned32(x) && aligned16(q);
     const int nwide = (int)(D / 16);
     int tpr = 32;
-    while (tpr < 256 && tpr * 4 < nwide) tpr *= 2;    // aim at 4 chunks (128 B in flight) per thread
+    while (tpr < 256 && tpr * 4 < nwide) tpr *= 2;    // aim at 4 chunks (128 B in flight) per thread; 2 and 8 measured slower
     const int n = (nwide + tpr - 1) / tpr;
     if (!wide_ok || n > 8) {
         quant_row_long_kernel<INT8><<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)q, scales, M, nchunks, ldx);
