@@ -90,7 +90,12 @@ struct GemmParams {
 // for more stages (more weight bytes in flight).  The MMA still reads 128 rows from the A base,
 // i.e. it runs on into whatever follows; those rows only feed accumulator rows >= M, which are
 // never stored.  kTailPad keeps that overrun of the last stage inside the allocation.
-template <int BN, int STAGES, bool kPair = false, int AROWS = BM>
+// SCALE_THREADS > 0 (block-scale epilogue with one weight scale per 128 columns): a scale area
+// behind the barriers holds, per epilogue thread and for two chunks of kScaleChunk K blocks, the
+// activation scales of the thread's row (thread-private float4 slots) and, per epilogue warp, the
+// chunk's weight scales.
+constexpr int kScaleChunk = 32;       // K blocks per chunk of staged scales
+template <int BN, int STAGES, bool kPair = false, int AROWS = BM, int SCALE_THREADS = 0>
 struct SmemLayout {
     static constexpr int kABytes = AROWS * BK;
     static constexpr int kTailPad = (BM - AROWS) * BK;
@@ -100,7 +105,12 @@ struct SmemLayout {
     static constexpr int kBarOffset = STAGES * kStageBytes;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
     static constexpr int kNumBars = 2 * STAGES + 4;
-    static constexpr int kTotal = kBarOffset + (kNumBars * 8 + 16 > kTailPad ? kNumBars * 8 + 16 : kTailPad);
+    static constexpr int kScaleOffset = kBarOffset + ((kNumBars * 8 + 16 + 15) / 16) * 16;
+    static constexpr int kSaBytes = 2 * (kScaleChunk / 4) * SCALE_THREADS * 16;     // [2][chunk/4][thread] float4
+    static constexpr int kSbBytes = 2 * (SCALE_THREADS / 32) * kScaleChunk * 4;     // [2][warp][chunk] float
+    static constexpr int kScaleBytes = kSaBytes + kSbBytes;
+    static constexpr int kTotal = SCALE_THREADS > 0 ? kScaleOffset + kScaleBytes
+                                                    : kBarOffset + (kNumBars * 8 + 16 > kTailPad ? kNumBars * 8 + 16 : kTailPad);
     static constexpr int kDynamic = kTotal + 1024;   // slack for the manual 1024-byte alignment
     static_assert(kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
@@ -168,9 +178,9 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
 template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM>
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-    using L = SmemLayout<BN, STAGES, kPair, AROWS>;
-    static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
+    using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0>;
+    static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
     constexpr int EPI_WARPS = 4 * EPI_GROUPS;
     constexpr int COLS_PER_GROUP = BN / EPI_GROUPS;
     constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
@@ -314,6 +324,46 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint32_t acc_ph = 0;
         bool ok = true;
         const bool wide = (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 31) == 0;
+        // staged scales (block-scale epilogue with 128-column weight-scale groups only)
+        constexpr int EPI_THREADS = 32 * EPI_WARPS;
+        float4* const sa_slots = reinterpret_cast<float4*>(smem + L::kScaleOffset) + (threadIdx.x - EPI_WARP0 * 32);
+        float* const sb_slots = reinterpret_cast<float*>(smem + L::kScaleOffset + L::kSaBytes) + ew * kScaleChunk;
+        int sbuf = 0;
+        // cp.async the scales of (tile, chunk) into buffer `buf`: this thread's row of a_scale as
+        // float4 slots [kb/4][thread], and lane l of each warp the weight scale of K block l of the
+        // warp's column group.  Completion is awaited by the same thread (sa) / warp (sb) only.
+        auto stage_scales = [&](int buf, int tile, int chunk) {
+            const int tb = tile / tiles_per_batch;
+            int tmb, tnb;
+            tile_coords(tile - tb * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, tmb, tnb);
+            int r = tmb * TILE_M + (int)rank * BM + row_in_tile;
+            if (r >= p.M) r = p.M - 1;
+            const int kb0 = chunk * kScaleChunk;
+            const float* src = p.sa + (int64_t)r * kblocks + kb0;
+            const uint32_t dst = smem_u32(sa_slots + (size_t)buf * (kScaleChunk / 4) * EPI_THREADS);
+            const bool vec = (kblocks % 4) == 0 && (reinterpret_cast<uintptr_t>(p.sa) & 15) == 0;
+#pragma unroll
+            for (int j = 0; j < kScaleChunk / 4; ++j) {
+                const int kb = kb0 + 4 * j;
+                const uint32_t d = dst + (uint32_t)j * EPI_THREADS * 16;
+                if (vec) {
+                    if (kb < kblocks) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + 4 * j) : "memory");
+                } else {
+                    for (int i = 0; i < 4; ++i)
+                        if (kb + i < kblocks) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d + 4 * i), "l"(src + 4 * j + i) : "memory");
+                }
+            }
+            const int nsb = p.N / 128;
+            const int cg = min((tnb * BN + grp * COLS_PER_GROUP) / 128, nsb - 1);
+            const int kb = kb0 + lane;
+            if (kb < kblocks)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
+                             ::"r"(smem_u32(sb_slots + (size_t)buf * EPI_WARPS * kScaleChunk + lane)), "l"(p.sb + (int64_t)kb * nsb + cg) : "memory");
+        };
+        if constexpr (kBlockScale && kGn128) {
+            if (tile0 < total_tiles) stage_scales(0, tile0, 0);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         for (int t = tile0; t < total_tiles && ok; t += tile_step) {
             const int b = t / tiles_per_batch;
             int mb, nb;
@@ -365,29 +415,31 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 64; ++j) acc2[j] = make_float2(0.0f, 0.0f);
                 const int kbs = kblocks;
-                const float* sarow = p.sa + (int64_t)(row_ok ? row : p.M - 1) * kbs;
-                const int nsb = p.N / 128;
-                const float* sbcol = p.sb + min(col_base / 128, nsb - 1);
-                // activation scales of this row, four K blocks per (row-strided, hence costly) load
-                const bool sa_vec = (kbs % 4) == 0;
-                auto load_sa4 = [&](int kb4) {
-                    if (kb4 >= kbs) return make_float4(0, 0, 0, 0);
-                    if (sa_vec) return __ldg(reinterpret_cast<const float4*>(sarow + kb4));
-                    float4 q = make_float4(__ldg(sarow + kb4), 0, 0, 0);
-                    if (kb4 + 1 < kbs) q.y = __ldg(sarow + kb4 + 1);
-                    if (kb4 + 2 < kbs) q.z = __ldg(sarow + kb4 + 2);
-                    if (kb4 + 3 < kbs) q.w = __ldg(sarow + kb4 + 3);
-                    return q;
-                };
-                float4 sa_cur = load_sa4(0), sa_nxt = load_sa4(4);
-                float sb_next = __ldg(sbcol);
-                for (int kb = 0; kb < kbs; ++kb) {
-                    const int sub = kb & 3;
-                    const float sa_k = sub == 0 ? sa_cur.x : sub == 1 ? sa_cur.y : sub == 2 ? sa_cur.z : sa_cur.w;
-                    const float sc = sa_k * sb_next;
+                // Scales come from shared memory: a global load in this loop, even one issued a K
+                // block ahead, returns after an L2 round trip that is as long as the K block itself
+                // and sets the pace of the whole MMA <-> epilogue hand-off.  cp.async stages the
+                // scales of the next chunk (32 K blocks; the next tile's first chunk at a tile's end)
+                // while this one is processed.
+                const int nchunks = (kbs + kScaleChunk - 1) / kScaleChunk;
+                for (int ch = 0; ch < nchunks && ok; ++ch) {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncwarp();
+                    {   // stage the scales that follow this chunk
+                        int nt = t, nch = ch + 1;
+                        if (nch == nchunks) { nt = t + tile_step; nch = 0; }
+                        if (nt < total_tiles) stage_scales(sbuf ^ 1, nt, nch);
+                        asm volatile("cp.async.commit_group;" ::: "memory");
+                    }
+                    const float4* sa_s = sa_slots + (size_t)sbuf * (kScaleChunk / 4) * EPI_THREADS;
+                    const float* sb_s = sb_slots + (size_t)sbuf * EPI_WARPS * kScaleChunk;
+                    const int kb_end = min(kbs - ch * kScaleChunk, kScaleChunk);
+                    float4 sa4 = sa_s[0];
+                for (int kk = 0; kk < kb_end; ++kk) {
+                    const int sub = kk & 3;
+                    const float sa_k = sub == 0 ? sa4.x : sub == 1 ? sa4.y : sub == 2 ? sa4.z : sa4.w;
+                    const float sc = sa_k * sb_s[kk];
                     const float2 s2 = make_float2(sc, sc);
-                    if (kb + 1 < kbs) sb_next = __ldg(sbcol + (int64_t)(kb + 1) * nsb);   // uniform address: one wavefront
-                    if (sub == 3) { sa_cur = sa_nxt; sa_nxt = load_sa4(kb + 5); }
+                    if (sub == 3 && kk + 1 < kb_end) sa4 = sa_s[(size_t)((kk + 1) >> 2) * EPI_THREADS];
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
@@ -413,6 +465,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc2[48 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[48 + j]);
                     if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+                    sbuf ^= 1;
                 }
                 if (ok && row_ok) {
                     // N % 128 == 0 in block-scale mode: rows are 32-byte aligned, whole groups are in range
@@ -469,6 +523,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 
     // ---- teardown: every role is done (or has given up); free TMEM ----
+    asm volatile("cp.async.wait_group 0;" ::: "memory");      // no staged-scale copy may outlive the CTA
     tc_fence_before();
     __syncthreads();
     if constexpr (kPair) { __syncwarp(); cluster_sync_all(); }   // the partner is done with this CTA's smem, barriers and TMEM
@@ -486,7 +541,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // CTA-pair launch: clusters of 2 along x, one cluster per pair of SMs, persistent over 256 x 256 tiles.
 template <int STAGES, bool kBlockScale>
 int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
-    using L = SmemLayout<256, STAGES, true>;
+    using L = SmemLayout<256, STAGES, true, BM, kBlockScale ? 256 : 0>;
+    static_assert(L::kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
     auto kern = gemm_fp8_kernel<256, STAGES, kBlockScale, true, true>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(e));
@@ -525,7 +581,8 @@ inline bool skinny_enabled() {
 
 template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
-    using L = SmemLayout<BN, STAGES, false, AROWS>;
+    using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0>;
+    static_assert(L::kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
     auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS>;
     // the attribute is per device; set it on every call (cheap) so multi-device processes work
     const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -655,13 +712,13 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
         p.m_blks = (int)((M + 255) / 256);
         rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, 128);
         if (rc != HKB_OK) return rc;
-        return launch_gemm_pair<7, true>(tmA, tmB, p, st);
+        return launch_gemm_pair<4, true>(tmA, tmB, p, st);
     }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
     if (gn == 128) {
-        if (bn == 256) return launch_gemm<256, 4, true, true>(tmA, tmB, p, st);
-        return launch_gemm<128, 6, true, true>(tmA, tmB, p, st);
+        if (bn == 256) return launch_gemm<256, 3, true, true>(tmA, tmB, p, st);
+        return launch_gemm<128, 5, true, true>(tmA, tmB, p, st);
     }
     return launch_gemm<128, 6, true, false>(tmA, tmB, p, st);
 }

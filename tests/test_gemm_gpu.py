@@ -207,7 +207,9 @@ def test_gemm_per_token_skinny_with_bias(hk):
 # ---- block scales ---------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("shape,gn", [((128, 128, 256), 1), ((128, 128, 128), 128), ((256, 256, 512), 128),
-                                      ((512, 512, 512), 1), ((200, 384, 1024), 128), ((1024, 4096, 2048), 128)])
+                                      ((512, 512, 512), 1), ((200, 384, 1024), 128), ((1024, 4096, 2048), 128),
+                                      # more than one 32-K-block chunk of staged scales: 36, 65 (odd) and 96 K blocks
+                                      ((128, 256, 4608), 128), ((256, 128, 8320), 128), ((384, 512, 12288), 128)])
 def test_gemm_blockscale_reference_scale_distribution(hk, shape, gn):
     """Shapes and scale distributions of the reference (tests/test_gemm.py:128-162: 128x128x256, gn=1;
     per-directory reference with generic gn), operands e4m3-representable."""
