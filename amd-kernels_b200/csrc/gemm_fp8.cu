@@ -63,6 +63,21 @@ int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint
     return HKB_OK;
 }
 
+int make_tmap_linear1k(CUtensorMap* map, const void* base, uint64_t bytes) {
+    load_encoder();
+    HKB_REQUIRE(g_encode != nullptr, HKB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    HKB_REQUIRE(aligned16(base) && bytes % 1024 == 0 && bytes > 0, HKB_ERR_BAD_ALIGN, "linear TMA view needs a 16-byte aligned base and a multiple of 1 KB");
+    const cuuint64_t dims[3] = {256, bytes / 256, 1};
+    const cuuint64_t strides[2] = {256, bytes};
+    const cuuint32_t box[3] = {256, 4, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    HKB_REQUIRE(r == CUDA_SUCCESS, HKB_ERR_CUDA, "cuTensorMapEncodeTiled (linear) failed with CUresult %d", (int)r);
+    return HKB_OK;
+}
+
 namespace {
 
 constexpr int BM = 128;        // tile rows = TMEM lanes

@@ -12,6 +12,8 @@
 // use it.
 //
 // Roles, ring, bounded waits and teardown are those of the FP8 kernel (gemm_fp8.cu).
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 #include <mutex>
@@ -284,6 +286,233 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
 }
 
+// ---- CTA pairs -------------------------------------------------------------------------------
+// Large problems: a cluster of two CTAs works on one 256 x 192 tile (tcgen05 cta_group::2).
+// Each CTA stages its own 128 rows of A, its own half (96 rows) of the tile's B rows, the scale
+// atoms of its own A rows and the scale atoms of ALL the tile's B rows: a third less operand
+// traffic from L2 per SM, which is what bounds the single-CTA kernel (its 148 SMs together pull
+// ~17.5 TB/s from L2).  The leader (even CTA) issues the scale copies and the MMAs for both CTAs;
+// completion bytes of both CTAs' loads are credited to the leader's barriers (tensor-map loads
+// in their cta_group::2 form, hence the scale atoms also travel through a -- linear -- tensor map);
+// commits are multicast to both CTAs; both epilogues release the accumulator on the leader's
+// barrier with a remote arrive.  No multicast loads anywhere.
+struct PairCfg {
+    static constexpr int BN = 192;
+    static constexpr int kStages = 7;
+    static constexpr int kABytes = BM * BKB;                  // 16 KB
+    static constexpr int kBBytes = (BN / 2) * BKB;            // 12 KB: this CTA's half of the B rows
+    static constexpr int kSfaOff = kABytes + kBBytes;
+    static constexpr int kSfbOff = kSfaOff + SF_STAGE;
+    static constexpr int kStageBytes = kSfbOff + 2 * SF_STAGE;   // 31 KB
+    static constexpr int kBarOffset = kStages * kStageBytes;
+    static constexpr int kNumBars = 2 * kStages + 4;
+    static constexpr int kDynamic = kBarOffset + kNumBars * 8 + 16 + 1024;
+    static constexpr uint32_t kTmemCols = 512;
+    static constexpr uint32_t kTmemSfa = 2 * BN;
+    static constexpr uint32_t kTmemSfb = 2 * BN + 8;
+    static_assert(kStageBytes % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
+    static_assert(kDynamic <= 232448, "shared memory budget");
+};
+
+struct Mxfp4PairParams {
+    Mxfp4Params g;                // m_blks counts 256-row blocks here
+    int sfa_rblks;                // 128-row blocks of A's scales per batch in the scratch (even)
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_mxfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmSfa, const __grid_constant__ CUtensorMap tmSfb,
+                       const Mxfp4PairParams pp) {
+    using Smem = PairCfg;
+    constexpr int BN = Smem::BN;
+    constexpr int STAGES = Smem::kStages;
+    constexpr uint32_t TMEM_COLS = Smem::kTmemCols, TMEM_SFA = Smem::kTmemSfa, TMEM_SFB = Smem::kTmemSfb;
+    const Mxfp4Params& p = pp.g;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + Smem::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::kBarOffset + Smem::kNumBars * 8);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int kstages = (p.K + 255) / 256;
+    const int tiles_per_batch = p.m_blks * p.n_blks;
+    const int total_tiles = tiles_per_batch * p.batch;
+    const int tile0 = (int)(blockIdx.x >> 1);
+    const int tile_step = (int)(gridDim.x >> 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);          // the leader hears both CTAs' four epilogue warps
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();        // the partner's barriers and TMEM exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            prefetch_tmap(&tmA);
+            prefetch_tmap(&tmB);
+            prefetch_tmap(&tmSfa);
+            prefetch_tmap(&tmSfb);
+            // the leader's full barrier counts the bytes of both CTAs' loads
+            constexpr uint32_t stage_tx = 2u * (Smem::kABytes + Smem::kBBytes + 3 * SF_STAGE);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+                const int b = t / tiles_per_batch;
+                int mb, nb;
+                tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M / 2, mb, nb);
+                // scratch rows (256 bytes each) of this CTA's A-scale block and of the tile's two B-scale atoms
+                const int64_t sfa_row0 = (((int64_t)b * pp.sfa_rblks + 2 * mb + (int)rank) * p.katoms) * 2;
+                const int atom0 = (nb * BN) >> 7;
+                const int64_t sfb_row0 = (((int64_t)b * p.sfb_rblks + atom0) * p.katoms) * 2;
+                for (int ks = 0; ks < kstages; ++ks) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t st = smem_base + s * Smem::kStageBytes;
+                    tma_load_3d_pair(st, &tmA, full_bar(s), ks * BKB, mb * 2 * BM + (int)rank * BM, b);
+                    tma_load_3d_pair(st + Smem::kABytes, &tmB, full_bar(s), ks * BKB, nb * BN + (int)rank * (BN / 2), b);
+                    tma_load_3d_pair(st + Smem::kSfaOff, &tmSfa, full_bar(s), 0, (int32_t)(sfa_row0 + (int64_t)ks * 4), 0);
+                    tma_load_3d_pair(st + Smem::kSfbOff, &tmSfb, full_bar(s), 0, (int32_t)(sfb_row0 + (int64_t)ks * 4), 0);
+                    tma_load_3d_pair(st + Smem::kSfbOff + SF_STAGE, &tmSfb, full_bar(s), 0,
+                                     (int32_t)(sfb_row0 + (int64_t)p.katoms * 2 + (int64_t)ks * 4), 0);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && elect_one()) {
+            int s = 0;
+            uint32_t ph = 0;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+                if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                const int b_ = t / tiles_per_batch;
+                int mb_, nb_;
+                tile_coords(t - b_ * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M / 2, mb_, nb_);
+                const int sf_off = ((nb_ * BN) >> 5) & 3;          // 0 or 2: first 32-row group of the tile inside its first atom
+                for (int ks = 0; ks < kstages; ++ks) {
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_base + s * Smem::kStageBytes;
+                    const uint64_t da = smem_desc_sw128(st);
+                    const uint64_t db = smem_desc_sw128(st + Smem::kABytes);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {      // the two 128-K atoms of this stage
+                        tc_cp_sf_pair(tmem_base + TMEM_SFA + h * 4, smem_desc_sf(st + Smem::kSfaOff + h * 512));
+#pragma unroll
+                        for (int r = 0; r < 2; ++r)
+                            tc_cp_sf_pair(tmem_base + TMEM_SFB + (h * 2 + r) * 4, smem_desc_sf(st + Smem::kSfbOff + r * SF_STAGE + h * 512));
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t h = k >> 1, sf_id = (k & 1) * 2;
+                        mma_mxf4_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_mxf4(2 * BM, BN, sf_id, sf_id),
+                                      tmem_base + TMEM_SFA + h * 4, tmem_base + TMEM_SFB + h * 2 * 4 + sf_off, (ks | k) != 0);
+                    }
+                    tc_commit_pair(empty_bar(s), 3);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (ok) {
+                    tc_commit_pair(tfull_bar(acc), 3);
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        int acc = 0;
+        uint32_t acc_ph = 0;
+        for (int t = tile0; t < total_tiles; t += tile_step) {
+            const int b = t / tiles_per_batch;
+            int mb, nb;
+            tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M / 2, mb, nb);
+            const int row = mb * 2 * BM + (int)rank * BM + row_in_tile;
+            const bool row_ok = row < p.M;
+            const int64_t row_off = ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
+            __nv_bfloat16* crow = p.C + row_off;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) break;
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + lane_addr + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(t_addr + c, r);
+                tmem_ld_wait();
+                if (row_ok) {
+                    const int col0 = nb * BN + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (col0 + j < p.N) {
+                            if (p.c_a) {
+                                float ca[8], cb[8];
+                                unpack8(__ldg(reinterpret_cast<const uint4*>(p.c_a + row_off + col0 + j)), ca);
+                                unpack8(__ldg(reinterpret_cast<const uint4*>(p.c_b + row_off + col0 + j)), cb);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) r[j + i] = __float_as_uint(__fmaf_rn(ca[i], __uint_as_float(r[j + i]), cb[i]));
+                            }
+                            uint4 o;
+                            __nv_bfloat162 q0 = __floats2bfloat162_rn(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
+                            __nv_bfloat162 q1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            __nv_bfloat162 q2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            __nv_bfloat162 q3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            o.x = *reinterpret_cast<uint32_t*>(&q0);
+                            o.y = *reinterpret_cast<uint32_t*>(&q1);
+                            o.z = *reinterpret_cast<uint32_t*>(&q2);
+                            o.w = *reinterpret_cast<uint32_t*>(&q3);
+                            *reinterpret_cast<uint4*>(crow + col0 + j) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_bar(acc), 0);
+            if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();        // the partner is done with this CTA's shared memory, barriers and TMEM
+    if (warp == 1) {
+        if (*abort_flag) {
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, const void* sfb, const void* c_a, const void* c_b,
                     int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
     HKB_REQUIRE(A && B && C && sfa && sfb, HKB_ERR_BAD_ARG, "gemm_mxfp4: null pointer");
@@ -313,17 +542,23 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
     int rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
 
+    // CTA pairs on 256 x 192 tiles when there is at least half a wave of them (HKB_MXFP4_PAIRS=0: never)
+    static const bool pairs_on = [] { const char* v = getenv("HKB_MXFP4_PAIRS"); return !(v && v[0] == '0'); }();
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 191) / 192) * batch;
+    const bool pair = pairs_on && wide && M > 128 && pair_tiles >= sms / 2 && sms >= 2;
+    const int sfa_rblks = pair ? 2 * (int)((M + 255) / 256) : p.m_blks;      // pairs address A's scale blocks as 2*mb + rank
+
     // scale re-layout into library-owned scratch (grown on demand, reused across calls)
     void *sfa_sw = nullptr, *sfb_sw = nullptr;
-    const size_t sfa_bytes = (size_t)batch * p.m_blks * p.katoms * 512;
+    const size_t sfa_bytes = (size_t)batch * sfa_rblks * p.katoms * 512;
     const size_t sfb_bytes = (size_t)batch * p.sfb_rblks * p.katoms * 512;
     rc = scratch_get(SCRATCH_SFA, sfa_bytes, &sfa_sw);
     if (rc != HKB_OK) return rc;
     rc = scratch_get(SCRATCH_SFB, sfb_bytes, &sfb_sw);
     if (rc != HKB_OK) return rc;
     {
-        dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)p.m_blks, (unsigned)batch);
-        sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)sfa, (uint8_t*)sfa_sw, (int)M, katoms_src, p.katoms, p.m_blks);
+        dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)sfa_rblks, (unsigned)batch);
+        sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)sfa, (uint8_t*)sfa_sw, (int)M, katoms_src, p.katoms, sfa_rblks);
         dim3 gb((unsigned)((p.katoms + 31) / 32), (unsigned)p.sfb_rblks, (unsigned)batch);
         sf_relayout_kernel<<<gb, 256, 0, st>>>((const uint8_t*)sfb, (uint8_t*)sfb_sw, (int)N, katoms_src, p.katoms, p.sfb_rblks);
         rc = check_launch("sf_relayout_kernel");
@@ -335,6 +570,38 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
     CUtensorMap tmA, tmB;
     rc = make_tmap_bytes(&tmA, A, (uint64_t)K / 2, (uint64_t)M, (uint64_t)batch, BM);
     if (rc != HKB_OK) return rc;
+    if (pair) {
+        Mxfp4PairParams pp{};
+        pp.g = p;
+        pp.g.m_blks = (int)((M + 255) / 256);
+        pp.sfa_rblks = sfa_rblks;
+        CUtensorMap tmSfa, tmSfb;
+        rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, PairCfg::BN / 2);
+        if (rc != HKB_OK) return rc;
+        rc = make_tmap_linear1k(&tmSfa, sfa_sw, sfa_bytes);
+        if (rc != HKB_OK) return rc;
+        rc = make_tmap_linear1k(&tmSfb, sfb_sw, sfb_bytes);
+        if (rc != HKB_OK) return rc;
+        cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kDynamic);
+        HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+        int clusters = sms / 2;
+        if (pair_tiles < clusters) clusters = (int)pair_tiles;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * clusters);
+        cfg.blockDim = dim3(192);
+        cfg.dynamicSmemBytes = PairCfg::kDynamic;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, gemm_mxfp4_pair_kernel, tmA, tmB, tmSfa, tmSfb, pp);
+        HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "launch of gemm_mxfp4_pair_kernel failed: %s", cudaGetErrorString(e));
+        return check_launch("gemm_mxfp4_pair_kernel");
+    }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
     const int tiles = p.m_blks * p.n_blks * p.batch;

@@ -14,6 +14,9 @@ namespace hkb {
 // Out-of-bounds rows/bytes read as zero, so M/N tails need no special casing in the kernels.
 int make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
                     uint64_t batch, uint32_t box_rows);
+// Unswizzled view of a byte array as rows of 256 bytes; box = 4 rows = 1 KB of contiguous bytes
+// landing contiguously in shared memory.  Coordinates: (0, byte offset / 256, 0).
+int make_tmap_linear1k(CUtensorMap* map, const void* base, uint64_t bytes);
 
 // Per-token-scale FP8 GEMM for M <= 64, batch 1, N % 16 == 0 (gemm_fp8_skinny.cu); arguments are
 // expected to be validated by the caller.  `status` is the device status word.
@@ -251,6 +254,17 @@ __device__ __forceinline__ void mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, ui
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_mxf4_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate) : "memory");
+}
+// Scale-atom copy in both CTAs of the pair: each from its own shared memory to its own TMEM.
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t tmem_dst, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
 }
 // Arrive on the barrier at this offset in CTA `cta` of the cluster.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
