@@ -66,7 +66,7 @@ L2_FLUSH_BYTES = 256 << 20
 # (profiles/ has the captures); None = not captured.
 NCU_TRAFFIC = {
     "c2": 290.1e6,       # profiles/c2_gemm_fp8_blockscale.md
-    "c3": 199.6e6,       # profiles/c3_gemm_mxfp4.md
+    "c3": 204.2e6,       # profiles/c3_gemm_mxfp4.md
     "c4a": 241.4e6,      # profiles/c4a_gemm_fp8_decode.md
     "c4b": 166.5e6,      # profiles/c4b_gemm_fp8_per_token_pairs.md
     "qbw-fp8": 373.3e6,  # profiles/qbw_quant_per_token_fp8.md
