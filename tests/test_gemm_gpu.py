@@ -284,7 +284,8 @@ def _mxfp4_operands(M, N, K, batch=1, seed=42):
 
 @pytest.mark.parametrize("shape", [(128, 128, 256), (128, 128, 128), (256, 256, 256), (1024, 1024, 1024),
                                    (200, 264, 512), (128, 128, 384), (512, 2048, 8192),
-                                   (2304, 3264, 256), (4096, 4680, 512)])        # wide (192-column) tiles, ragged N
+                                   (2304, 3264, 256), (4096, 4680, 512),         # wide (192-column) tiles, ragged N
+                                   (2400, 3072, 256), (2432, 3080, 384)])        # CTA pairs whose last row block is partial / half empty
 def test_gemm_mxfp4(hk, shape):
     M, N, K = shape
     ac, wc, asc, wsc = _mxfp4_operands(M, N, K)
