@@ -62,7 +62,7 @@ __device__ __forceinline__ uint2 encode8_f32(const float (&f)[8], const Divider2
 // A CTA of 256 threads covers 256/TPR rows; TPR threads share a row and each holds NW 32-byte
 // chunks (chunk index = t + i*TPR) in registers.  Needs D % 16 == 0 and 32-byte aligned rows.
 template <int NW, int TPR, bool INT8>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, NW <= 4 ? 4 : 2)
 quant_row_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                  float* __restrict__ scales, int64_t M, int nwide, int64_t ldx) {
     constexpr int RPB = 256 / TPR;
