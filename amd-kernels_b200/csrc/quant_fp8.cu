@@ -225,57 +225,98 @@ quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
 }
 
 // Fused RMSNorm prologue: y = x * rsqrt(mean(x^2) + eps) * w in fp32, then the 1x128 rule on y.
-// One CTA per row; the row stays in registers as bf16 chunks.
-template <int NCHUNK>
-__global__ void __launch_bounds__(256)
+// Fused RMSNorm prologue: y = x * rsqrt(mean(x^2) + eps) * w in fp32, then the 1x128 rule on y.
+// Same thread layout as quant_row_kernel: TPR threads share a row, each keeps NW 32-byte chunks
+// (chunk index t + i*TPR) in registers between the sum-of-squares pass and the encode pass; the
+// eight chunks of a 128-element group sit in eight neighbouring lanes, so the group maximum is
+// three shuffles.  Rows of a CTA meet only on their own named barrier.
+template <int NW, int TPR>
+__global__ void __launch_bounds__(256, NW <= 4 ? 3 : 2)
 rmsnorm_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                           uint8_t* __restrict__ q, float* __restrict__ scales, int nchunks, float eps) {
-    const int64_t row = blockIdx.x;
-    const int t = threadIdx.x;
-    const __nv_bfloat16* xr = x + row * (int64_t)nchunks * 8;
-    uint4 v[NCHUNK];
-    float ss = 0.0f;
+                           uint8_t* __restrict__ q, float* __restrict__ scales, int64_t M, int nwide, float eps) {
+    constexpr int RPB = 256 / TPR;
+    const int tid = threadIdx.x;
+    const int r_in = tid / TPR;
+    const int t = tid % TPR;
+    const int64_t row = (int64_t)blockIdx.x * RPB + r_in;
+    const bool live = row < M;
+    const __nv_bfloat16* xr = x + row * ((int64_t)nwide * 16);
+
+    Wide v[NW];
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
-        const int c = t + i * 256;
-        v[i] = (c < nchunks) ? ld_stream16(xr + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
-        float f[8];
-        unpack8(v[i], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss = __fmaf_rn(f[j], f[j], ss);
+    for (int i = 0; i < NW; ++i) {
+        const int c = t + i * TPR;
+        v[i] = (live && c < nwide) ? ld_stream32(xr + (int64_t)c * 16) : wide_zero();
     }
+    float2 ss2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        const uint32_t xw[8] = {v[i].lo.x, v[i].lo.y, v[i].lo.z, v[i].lo.w, v[i].hi.x, v[i].hi.y, v[i].hi.z, v[i].hi.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float2 f = bf16x2_to_f2(xw[j]); ss2 = __ffma2_rn(f, f, ss2); }
+    }
+    float ss = ss2.x + ss2.y;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-    __shared__ float s_ss[8];
-    if ((t & 31) == 0) s_ss[t >> 5] = ss;
-    __syncthreads();
-    ss = 0.0f;
+    if constexpr (TPR > 32) {
+        __shared__ float s_ss[8];
+        if ((tid & 31) == 0) s_ss[tid >> 5] = ss;
+        if constexpr (TPR == 256) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + r_in), "r"(TPR) : "memory");
+        constexpr int WPR = TPR / 32;
+        ss = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) ss += s_ss[k];
-    const float rinv = rsqrtf(ss / (float)(nchunks * 8) + eps);
+        for (int k = 0; k < WPR; ++k) ss += s_ss[r_in * WPR + k];
+    }
+    const float rinv = rsqrtf(ss / (float)(nwide * 16) + eps);
+    uint8_t* qr = q + row * ((int64_t)nwide * 16);
+    float* sr = scales + row * (int64_t)(nwide / 8);
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
-        const int c = t + i * 256;
-        const bool ok = c < nchunks;
-        float f[8], g[8];
-        unpack8(v[i], f);
-        const uint4 wv = ok ? *reinterpret_cast<const uint4*>(w + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
-        unpack8(wv, g);
+    for (int i = 0; i < NW; ++i) {
+        const int c = t + i * TPR;
+        const bool ok = live && c < nwide;
+        const uint4 w0 = ok ? __ldg(reinterpret_cast<const uint4*>(w + (int64_t)c * 16)) : make_uint4(0, 0, 0, 0);
+        const uint4 w1 = ok ? __ldg(reinterpret_cast<const uint4*>(w + (int64_t)c * 16 + 8)) : make_uint4(0, 0, 0, 0);
+        const uint32_t xw[8] = {v[i].lo.x, v[i].lo.y, v[i].lo.z, v[i].lo.w, v[i].hi.x, v[i].hi.y, v[i].hi.z, v[i].hi.w};
+        const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float2 rinv2 = make_float2(rinv, rinv);
+        float2 y[8];
         float am = 0.0f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            f[j] = f[j] * rinv * g[j];
-            am = fmaxf(am, fabsf(f[j]));
+            y[j] = __fmul2_rn(__fmul2_rn(bf16x2_to_f2(xw[j]), rinv2), bf16x2_to_f2(ww[j]));
+            am = fmaxf(am, fmaxf(fabsf(y[j].x), fabsf(y[j].y)));
         }
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+        for (int o = 4; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
         const float scale = fmaxf(__fdiv_rn(am, kFp8Max), kScaleFloor);
-        const Divider2 div(scale);
+        // y is only defined up to the order of the sum of squares, so the quotient is taken as
+        // y * RN(1/scale) (within one fp32 ulp of the true division) and the sign of a zero is
+        // left to the conversion: the exactly rounded division of the other quantizers buys
+        // nothing here and costs two more packed FMAs per pair.
+        const float rs = __frcp_rn(scale);
+        const float2 rs2 = make_float2(rs, rs);
         if (ok) {
-            *reinterpret_cast<uint2*>(q + (row * nchunks + c) * 8) = encode8_f32(f, div);
-            if ((t & 15) == 0) scales[(row * nchunks + c) >> 4] = scale;
+            uint32_t o4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 qa = __fmul2_rn(y[2 * j], rs2), qb = __fmul2_rn(y[2 * j + 1], rs2);
+                o4[j] = (uint32_t)cvt_e4m3x2(qa.x, qa.y) | ((uint32_t)cvt_e4m3x2(qb.x, qb.y) << 16);
+            }
+            *reinterpret_cast<uint4*>(qr + (int64_t)c * 16) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            if ((t & 7) == 0) sr[c >> 3] = scale;
         }
     }
+}
+
+template <int TPR>
+int launch_rms_1x128(int n, const void* x, const void* w, void* q, float* scales, int64_t M, int nwide, float eps, cudaStream_t st) {
+    constexpr int RPB = 256 / TPR;
+    const unsigned grid = (unsigned)((M + RPB - 1) / RPB);
+#define HKB_RMS(NWV) rmsnorm_quant_1x128_kernel<NWV, TPR><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)q, scales, M, nwide, eps)
+    if (n <= 1) HKB_RMS(1); else if (n <= 2) HKB_RMS(2); else if (n <= 4) HKB_RMS(4); else HKB_RMS(8);
+#undef HKB_RMS
+    return check_launch("rmsnorm_quant_1x128_kernel");
 }
 
 // ---- 128x128 ---------------------------------------------------------------------------
@@ -334,13 +375,17 @@ int hkb_quant_fp8_1x128(const void* x, const void* w, void* q, float* scales, in
     if (M == 0) return HKB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (w) {
-        const int nchunks = (int)(D / 8);
         HKB_REQUIRE(D <= 32768 && M <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_fp8_1x128 with RMSNorm: D must be <= 32768");
-        const int n = (nchunks + 255) / 256;
-#define HKB_RMS(NC) rmsnorm_quant_1x128_kernel<NC><<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)q, scales, nchunks, eps)
-        if (n <= 1) HKB_RMS(1); else if (n <= 2) HKB_RMS(2); else if (n <= 4) HKB_RMS(4); else if (n <= 8) HKB_RMS(8); else HKB_RMS(16);
-#undef HKB_RMS
-        return check_launch("rmsnorm_quant_1x128_kernel");
+        const int nwide = (int)(D / 16);
+        int tpr = 32;
+        while (tpr < 256 && tpr * 4 < nwide) tpr *= 2;       // 4 chunks per thread, as in the per-row quantizer
+        const int n = (nwide + tpr - 1) / tpr;
+        switch (tpr) {
+            case 32: return launch_rms_1x128<32>(n, x, w, q, scales, M, nwide, eps, st);
+            case 64: return launch_rms_1x128<64>(n, x, w, q, scales, M, nwide, eps, st);
+            case 128: return launch_rms_1x128<128>(n, x, w, q, scales, M, nwide, eps, st);
+            default: return launch_rms_1x128<256>(n, x, w, q, scales, M, nwide, eps, st);
+        }
     }
     constexpr int ITER = 2;
     const int64_t groups = M * (D / 128);

@@ -123,64 +123,126 @@ quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ co
     }
 }
 
-// Fused RMSNorm prologue (fp32 values, explicit compares); one CTA per row.
-template <int NCHUNK>
-__global__ void __launch_bounds__(256)
+// Fused RMSNorm prologue: y = x * rsqrt(mean(x^2) + eps) * w in fp32, then the MXFP4 rule on y.
+// Thread layout of the per-row FP8 quantizer: TPR threads share a row, each keeps NW 32-byte
+// chunks (chunk index t + i*TPR) in registers between the sum-of-squares pass and the encode
+// pass; the two chunks of a 32-element block sit in neighbouring lanes.  Rows of a CTA meet only
+// on their own named barrier.  Mode "doc" converts with the hardware round-to-nearest-even after
+// shrinking by (1 - 2^-22), which sends exact ties to the smaller magnitude (y is fp32 here, so
+// unlike the bf16 path a value within four ulps above a tie point can also land below it).
+template <int NW, int TPR, int MODE>
+__global__ void __launch_bounds__(256, NW <= 4 ? 3 : 2)
 rmsnorm_quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                           int nchunks, float eps, int mode) {
-    const int64_t row = blockIdx.x;
-    const int t = threadIdx.x;
-    const __nv_bfloat16* xr = x + row * (int64_t)nchunks * 8;
-    uint4 v[NCHUNK];
-    float ss = 0.0f;
+                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int64_t M, int nwide, float eps) {
+    constexpr int RPB = 256 / TPR;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int r_in = tid / TPR;
+    const int t = tid % TPR;
+    const int64_t row = (int64_t)blockIdx.x * RPB + r_in;
+    const bool live = row < M;
+    const __nv_bfloat16* xr = x + row * ((int64_t)nwide * 16);
+
+    Wide v[NW];
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
-        const int c = t + i * 256;
-        v[i] = (c < nchunks) ? ld_stream16(xr + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
-        float f[8];
-        unpack8(v[i], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss = __fmaf_rn(f[j], f[j], ss);
+    for (int i = 0; i < NW; ++i) {
+        const int c = t + i * TPR;
+        v[i] = (live && c < nwide) ? ld_stream32(xr + (int64_t)c * 16) : wide_zero();
     }
+    float2 ss2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        const uint32_t xw[8] = {v[i].lo.x, v[i].lo.y, v[i].lo.z, v[i].lo.w, v[i].hi.x, v[i].hi.y, v[i].hi.z, v[i].hi.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float2 f = bf16x2_to_f2(xw[j]); ss2 = __ffma2_rn(f, f, ss2); }
+    }
+    float ss = ss2.x + ss2.y;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-    __shared__ float s_ss[8];
-    if ((t & 31) == 0) s_ss[t >> 5] = ss;
-    __syncthreads();
-    ss = 0.0f;
+    if constexpr (TPR > 32) {
+        __shared__ float s_ss[8];
+        if ((tid & 31) == 0) s_ss[tid >> 5] = ss;
+        if constexpr (TPR == 256) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + r_in), "r"(TPR) : "memory");
+        constexpr int WPR = TPR / 32;
+        ss = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) ss += s_ss[k];
-    const float rinv = rsqrtf(ss / (float)(nchunks * 8) + eps);
-    const int64_t row_chunks = (int64_t)nchunks;
+        for (int k = 0; k < WPR; ++k) ss += s_ss[r_in * WPR + k];
+    }
+    const float rinv = rsqrtf(ss / (float)(nwide * 16) + eps);
+    uint8_t* cr = codes + row * ((int64_t)nwide * 8);
+    uint8_t* sr = scales + row * (int64_t)(nwide / 2);
+    const bool words = (nwide & 7) == 0;          // rows made of whole 128-element groups: scale bytes leave four at a time
 #pragma unroll
-    for (int i = 0; i < NCHUNK; ++i) {
-        const int c = t + i * 256;
-        const bool ok = c < nchunks;
-        float f[8], g[8];
-        unpack8(v[i], f);
-        const uint4 wv = ok ? *reinterpret_cast<const uint4*>(w + (int64_t)c * 8) : make_uint4(0, 0, 0, 0);
-        unpack8(wv, g);
+    for (int i = 0; i < NW; ++i) {
+        const int c = t + i * TPR;
+        const bool ok = live && c < nwide;
+        const uint4 w0 = ok ? __ldg(reinterpret_cast<const uint4*>(w + (int64_t)c * 16)) : make_uint4(0, 0, 0, 0);
+        const uint4 w1 = ok ? __ldg(reinterpret_cast<const uint4*>(w + (int64_t)c * 16 + 8)) : make_uint4(0, 0, 0, 0);
+        const uint32_t xw[8] = {v[i].lo.x, v[i].lo.y, v[i].lo.z, v[i].lo.w, v[i].hi.x, v[i].hi.y, v[i].hi.z, v[i].hi.w};
+        const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float2 rinv2 = make_float2(rinv, rinv);
+        float2 y[8];
         float am = 0.0f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            f[j] = f[j] * rinv * g[j];
-            am = fmaxf(am, fabsf(f[j]));
+            y[j] = __fmul2_rn(__fmul2_rn(bf16x2_to_f2(xw[j]), rinv2), bf16x2_to_f2(ww[j]));
+            am = fmaxf(am, fmaxf(fabsf(y[j].x), fabsf(y[j].y)));
         }
         am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 1));
-        am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, 2));
         uint32_t sb;
         float inv;
-        if (mode == HKB_MXFP4_MODE_KERNEL) block_exponent<HKB_MXFP4_MODE_KERNEL>(am, sb, inv);
-        else block_exponent<HKB_MXFP4_MODE_DOC>(am, sb, inv);
-        uint32_t out = 0;
+        block_exponent<MODE>(am, sb, inv);
+        uint32_t c0 = 0, c1 = 0;
+        if constexpr (MODE == HKB_MXFP4_MODE_KERNEL) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) out |= nibble_compare(f[j] * inv, mode) << (4 * j);
-        const int64_t gc = row * row_chunks + c;
-        if (ok) {
-            *reinterpret_cast<uint32_t*>(codes + gc * 4) = out;
-            if ((t & 3) == 0) scales[gc >> 2] = (uint8_t)sb;
+            for (int j = 0; j < 4; ++j) {
+                c0 |= (nibble_compare(y[j].x * inv, MODE) | (nibble_compare(y[j].y * inv, MODE) << 4)) << (8 * j);
+                c1 |= (nibble_compare(y[4 + j].x * inv, MODE) | (nibble_compare(y[4 + j].y * inv, MODE) << 4)) << (8 * j);
+            }
+        } else {
+            const float invs = inv * (1.0f - 0x1p-22f);
+            const float2 invs2 = make_float2(invs, invs), z2 = make_float2(0.0f, 0.0f);
+            float r[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 m = __ffma2_rn(y[j], invs2, z2); r[2 * j] = m.x; r[2 * j + 1] = m.y; }
+            c0 = cvt_e2m1x8(r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 m = __ffma2_rn(y[4 + j], invs2, z2); r[2 * j] = m.x; r[2 * j + 1] = m.y; }
+            c1 = cvt_e2m1x8(r);
         }
+        if (ok) *reinterpret_cast<uint2*>(cr + (int64_t)c * 8) = make_uint2(c0, c1);
+        // scale bytes of the four blocks held by lanes 8k .. 8k+7
+        const int l8 = lane & 24;
+        const uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, l8) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 2) << 8) |
+                              (__shfl_sync(0xFFFFFFFFu, sb, l8 + 4) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 6) << 24);
+        if (ok) {
+            if (words) { if ((t & 7) == 0) *reinterpret_cast<uint32_t*>(sr + (c >> 1)) = word; }
+            else if ((t & 1) == 0) sr[c >> 1] = (uint8_t)sb;
+        }
+    }
+}
+
+template <int TPR, int MODE>
+int launch_rms_mxfp4(int n, const void* x, const void* w, void* codes, void* scales, int64_t M, int nwide, float eps, cudaStream_t st) {
+    constexpr int RPB = 256 / TPR;
+    const unsigned grid = (unsigned)((M + RPB - 1) / RPB);
+#define HKB_RMS(NWV) rmsnorm_quant_mxfp4_kernel<NWV, TPR, MODE><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)codes, (uint8_t*)scales, M, nwide, eps)
+    if (n <= 1) HKB_RMS(1); else if (n <= 2) HKB_RMS(2); else if (n <= 4) HKB_RMS(4); else HKB_RMS(8);
+#undef HKB_RMS
+    return check_launch("rmsnorm_quant_mxfp4_kernel");
+}
+
+template <int MODE>
+int dispatch_rms_mxfp4(const void* x, const void* w, void* codes, void* scales, int64_t M, int nwide, float eps, cudaStream_t st) {
+    int tpr = 32;
+    while (tpr < 256 && tpr * 4 < nwide) tpr *= 2;
+    const int n = (nwide + tpr - 1) / tpr;
+    switch (tpr) {
+        case 32: return launch_rms_mxfp4<32, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
+        case 64: return launch_rms_mxfp4<64, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
+        case 128: return launch_rms_mxfp4<128, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
+        default: return launch_rms_mxfp4<256, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
     }
 }
 
@@ -198,13 +260,10 @@ extern "C" int hkb_quant_mxfp4(const void* x, const void* w, void* codes, void* 
     if (M == 0) return HKB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (w) {
-        const int nchunks = (int)(D / 8);
         HKB_REQUIRE(D <= 32768 && M <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_mxfp4 with RMSNorm: D must be <= 32768");
-        const int n = (nchunks + 255) / 256;
-#define HKB_RMS(NC) rmsnorm_quant_mxfp4_kernel<NC><<<(unsigned)M, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)codes, (uint8_t*)scales, nchunks, eps, mode)
-        if (n <= 1) HKB_RMS(1); else if (n <= 2) HKB_RMS(2); else if (n <= 4) HKB_RMS(4); else if (n <= 8) HKB_RMS(8); else HKB_RMS(16);
-#undef HKB_RMS
-        return check_launch("rmsnorm_quant_mxfp4_kernel");
+        const int nwide = (int)(D / 16);
+        if (mode == HKB_MXFP4_MODE_KERNEL) return dispatch_rms_mxfp4<HKB_MXFP4_MODE_KERNEL>(x, w, codes, scales, M, nwide, eps, st);
+        return dispatch_rms_mxfp4<HKB_MXFP4_MODE_DOC>(x, w, codes, scales, M, nwide, eps, st);
     }
     constexpr int ITER = 4;
     const int64_t blocks = M * (D / 32);

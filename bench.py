@@ -53,6 +53,9 @@ WORKLOADS = {
     "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
     "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),
     "qbw-mxfp4-16k": ("quant-mxfp4", 1, 16384, 0, 8192),
+    # the same two quantizers with the RMSNorm prologue (weight given)
+    "qbw-rms-1x128": ("quant-rms-1x128", 1, 16384, 0, 8192),
+    "qbw-rms-mxfp4": ("quant-rms-mxfp4", 1, 16384, 0, 8192),
     # quant_moe_tk casts (static FP8, MX FP8 / FP4 down-cast, MX FP8 up-cast)
     "qbw-moe-static": ("quant-moe-static", 1, 16384, 0, 8192),
     "qbw-moe-mxfp8": ("quant-moe-mxfp8", 1, 16384, 0, 8192),
@@ -150,7 +153,7 @@ def flops_of(kind, batch, M, N, K):
 def quant_bytes(kind, M, D):
     if kind == "quant-fp8":
         return M * D * 3 + M * 4
-    if kind == "quant-1x128":
+    if kind in ("quant-1x128", "quant-rms-1x128"):
         return M * D * 3 + M * (D // 128) * 4
     if kind == "quant-moe-static":
         return M * D * 3
@@ -183,7 +186,8 @@ class Workload:
         if self.kind.startswith("quant"):
             self.N = 0
             self.x = torch.randn(M, K, generator=g, device=dev, dtype=torch.float32).bfloat16()
-            if self.kind in ("quant-mxfp4", "quant-moe-mxfp4"):
+            self.w = torch.ones(K, dtype=torch.bfloat16, device=dev) if self.kind.startswith("quant-rms") else None
+            if self.kind in ("quant-mxfp4", "quant-moe-mxfp4", "quant-rms-mxfp4"):
                 self.q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
                 self.s = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
             elif self.kind.startswith("quant-moe"):
@@ -252,8 +256,10 @@ class Workload:
             hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
         elif self.kind == "quant-fp8":
             hk.per_token_quant_fwd(self.x, self.q, self.s)
-        elif self.kind == "quant-1x128":
-            hk.fused_rmsnorm_fp8_quant_fwd(self.x, None, self.q, self.s, 1e-6)
+        elif self.kind in ("quant-1x128", "quant-rms-1x128"):
+            hk.fused_rmsnorm_fp8_quant_fwd(self.x, self.w, self.q, self.s, 1e-6)
+        elif self.kind == "quant-rms-mxfp4":
+            hk.fused_rmsnorm_mxfp4_quant_fwd(self.x, self.w, self.q, self.s, 1e-6)
         elif self.kind == "quant-moe-static":
             hk.moe_routing.quant.downcast_to_static_fp8(self.x, self.q, self.s, self.M, K)
         elif self.kind == "quant-moe-mxfp8":
@@ -425,6 +431,7 @@ def cpu_reference_step(name, sample_rows):
     """One pass of the path on the CPU with the oracle (torch CPU + NumPy), on `sample_rows` rows
     of the activations and at most CPU_SAMPLE_MAX_N weight rows (all of K).
     Returns (seconds, units of work done, unit)."""
+    import numpy as np
     from oracle import gemm as ogemm, quant as oquant, quant_moe as omoe
     kind, B, M, N, K = WORKLOADS[name]
     if N > CPU_SAMPLE_MAX_N:
@@ -461,6 +468,10 @@ def cpu_reference_step(name, sample_rows):
         C = oquant.quant_fp8_per_token(A)
     elif kind == "quant-1x128":
         C = oquant.quant_fp8_1x128(A)
+    elif kind == "quant-rms-1x128":
+        C = oquant.quant_fp8_1x128(A, np.ones(K, dtype=np.float32))
+    elif kind == "quant-rms-mxfp4":
+        C = oquant.quant_mxfp4(A, np.ones(K, dtype=np.float32))
     elif kind == "quant-moe-static":
         C = omoe.downcast_to_static_fp8(A, 0.01)
     elif kind in ("quant-moe-mxfp8", "quant-moe-mxfp4"):
