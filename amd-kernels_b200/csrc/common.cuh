@@ -41,11 +41,21 @@ int sm_count();
 
 // Per-device, lazily grown scratch owned by the library (freed by hkb_release()).
 // `slot` separates independent users so they do not overwrite each other.
-enum ScratchSlot { SCRATCH_SFA = 0, SCRATCH_SFB = 1, SCRATCH_SPLITK = 2, SCRATCH_SLOTS = 3 };
-int scratch_get(ScratchSlot slot, size_t bytes, void** out);
+enum ScratchSlot { SCRATCH_SFA = 0, SCRATCH_SFB = 1, SCRATCH_SLOTS = 2 };
+// Scratch is keyed by (device, stream): calls on different streams of one device get different
+// blocks, so they may overlap on the GPU.  A device keeps blocks for up to kScratchStreams streams;
+// when more streams than that use scratch, the least recently used stream's blocks are recycled
+// (after a device-wide synchronisation, which cudaFree implies).
+constexpr int kScratchStreams = 8;
+int scratch_get(ScratchSlot slot, cudaStream_t stream, size_t bytes, void** out);
 // Device status word (one uint32 per device): kernels OR an error bit in when a bounded
 // wait runs out.  Zeroed at allocation.
 int status_word(uint32_t** out);
+// Name of the kernel variant the calling thread launched last (hkb_last_kernel()).
+void note_kernel(const char* name);
+// Status word of the allocation-free MXFP4 entry point on the current device, or null when that
+// entry point has not run on it (gemm_mxfp4.cu).
+uint32_t* static_status_peek();
 
 }  // namespace hkb
 

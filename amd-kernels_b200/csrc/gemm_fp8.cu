@@ -97,6 +97,8 @@ struct GemmParams {
     const __nv_bfloat16* c_a;  // blockscale only: fused epilogue C = c_a * gemm + c_b, both [M, N]; null = plain
     const __nv_bfloat16* c_b;
     uint32_t* status;
+    uint64_t wait_ns;          // limit of every mbarrier wait (kWaitLimitNs in production)
+    int skip_kblock;           // >= 0: the producer leaves this K block of its first tile unloaded (wait-limit probe only)
 };
 
 // kPair: two CTAs (a cluster of 2) share one 256 x BN tile; each stages its own 128 rows of A
@@ -265,8 +267,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 int mb, nb;
                 tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, mb, nb);
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer, p.wait_ns)) { ok = false; break; }
                     const uint32_t sa = smem_base + s * L::kStageBytes;
+                    if (p.skip_kblock == kb && t == tile0) {
+                        // wait-limit probe: nothing is loaded and nothing will arrive on this stage's barrier
+                        if (++s == STAGES) { s = 0; ph ^= 1; }
+                        continue;
+                    }
                     if constexpr (kPair) {
                         if (rank == 0) mbar_arrive_expect_tx(full_bar(s), stage_tx);
                         tma_load_3d_pair(sa, &tmA, full_bar(s), kb * BK, mb * TILE_M + (int)rank * BM, b);
@@ -290,15 +297,15 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             for (int t = tile0; t < total_tiles && ok; t += tile_step) {
                 if (!kBlockScale) {
-                    if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                    if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
                     tc_fence_after();
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (kBlockScale) {
-                        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
                         tc_fence_after();
                     }
-                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * L::kStageBytes;
                     const uint64_t da = smem_desc_sw128(sa);
@@ -392,7 +399,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const float sa = row_ok ? __ldg(p.sa + (int64_t)b * p.M + row) : 0.0f;
                 const float* sbp = p.sb + (int64_t)b * p.N;
                 const __nv_bfloat16* biasp = p.bias ? p.bias + (int64_t)b * p.N : nullptr;
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue, p.wait_ns))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
 #pragma unroll 1
@@ -455,7 +462,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const float sc = sa_k * sb_s[kk];
                     const float2 s2 = make_float2(sc, sc);
                     if (sub == 3 && kk + 1 < kb_end) sa4 = sa_s[(size_t)((kk + 1) >> 2) * EPI_THREADS];
-                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue, p.wait_ns))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
                     uint32_t ra[32], rb[32];
@@ -507,7 +514,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const float sa = sa_next;
                     if (kb + 1 < kbs) sa_next = __ldg(sarow + kb + 1);
                     const float* sbrow = p.sb + (int64_t)kb * nsb;
-                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) { ok = false; break; }
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue, p.wait_ns))) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
 #pragma unroll
@@ -580,6 +587,7 @@ int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmP
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p);
     HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cluster launch of gemm_fp8_kernel failed: %s", cudaGetErrorString(e));
+    note_kernel(kBlockScale ? "gemm_fp8_kernel<256,blockscale,pair>" : "gemm_fp8_kernel<256,pts,pair>");
     return check_launch("gemm_fp8_kernel (CTA pairs)");
 }
 
@@ -607,6 +615,8 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, gemm_threads<BN, kBlockScale>(), L::kDynamic, st>>>(tmA, tmB, p);
+    note_kernel(kBlockScale ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale>" : kGn128 ? "gemm_fp8_kernel<128,blockscale>" : "gemm_fp8_kernel<128,blockscale,gn1>")
+                            : (BN == 256 ? "gemm_fp8_kernel<256,pts>" : BN == 128 ? "gemm_fp8_kernel<128,pts>" : "gemm_fp8_kernel<64,pts>"));
     return check_launch("gemm_fp8_kernel");
 }
 
@@ -625,25 +635,29 @@ int common_checks(const char* who, const void* A, const void* B, const void* C, 
 
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                              const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream);
-}  // namespace hkb
 
-extern "C" {
-
-int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, const float* sb, const void* bias,
-                     int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
-    using namespace hkb;
+// wait_ns / skip_kblock: production passes kWaitLimitNs / -1; the wait-limit probe a short limit
+// and a K block that the producer leaves unloaded.
+int gemm_fp8_pts_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, const void* bias,
+                      int64_t batch, int64_t M, int64_t N, int64_t K, void* stream, uint64_t wait_ns, int skip_kblock) {
     int rc = common_checks("gemm_fp8_pts", A, B, C, batch, M, N, K);
     if (rc != HKB_OK) return rc;
     HKB_REQUIRE(sa && sb, HKB_ERR_BAD_ARG, "gemm_fp8_pts: null scale pointer");
+    // the epilogues read b_scale four floats and the bias eight bf16 at a time
+    HKB_REQUIRE((reinterpret_cast<uintptr_t>(sa) & 3) == 0 && aligned16(sb) && (!bias || aligned16(bias)), HKB_ERR_BAD_ALIGN,
+                "gemm_fp8_pts: a_scale must be 4-byte, b_scale and bias 16-byte aligned");
     GemmParams p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.sa = sa; p.sb = sb; p.bias = (const __nv_bfloat16*)bias; p.C = (__nv_bfloat16*)C; p.gn = 0;
+    p.wait_ns = wait_ns; p.skip_kblock = skip_kblock;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
     // Decode shapes: HBM-bound on the weight stream; a kernel that deals the columns out evenly
     // over the SMs (gemm_fp8_skinny.cu).  HKB_GEMM_SKINNY=0 keeps the fixed-width tiles below.
-    if (M <= 64 && batch == 1 && N % 16 == 0 && aligned32(C) && aligned16(sb) && (!bias || aligned16(bias)) && skinny_enabled())
+    if (M <= 64 && batch == 1 && N % 16 == 0 && aligned32(C) && skip_kblock < 0 && skinny_enabled()) {
+        note_kernel("gemm_fp8_skinny_kernel");
         return launch_gemm_fp8_skinny(A, B, C, sa, sb, bias, M, N, K, p.status, (cudaStream_t)stream);
+    }
     p.m_blks = (int)((M + BM - 1) / BM);
     // Skinny M: fetch only the rows that exist (rounded up to 8); the remaining rows of the
     // smem tile hold stale bytes that only reach accumulator rows >= M, which are never stored.
@@ -677,6 +691,22 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
     if (p.a_box_rows <= 64) return launch_gemm<64, 12, false, false, 64>(tmA, tmB, p, st);
     return launch_gemm<64, 8, false>(tmA, tmB, p, st);
 }
+}  // namespace hkb
+
+extern "C" {
+
+int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, const float* sb, const void* bias,
+                     int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+    return hkb::gemm_fp8_pts_impl(A, B, C, sa, sb, bias, batch, M, N, K, stream, hkb::kWaitLimitNs, -1);
+}
+
+int hkb_debug_gemm_fp8_wait_probe(const void* A, const void* B, void* C, const float* sa, const float* sb,
+                                  int64_t M, int64_t N, int64_t K, uint64_t wait_limit_ns, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(wait_limit_ns >= 1000 && wait_limit_ns <= kWaitLimitNs, HKB_ERR_BAD_ARG,
+                "gemm_fp8_wait_probe: the wait limit must lie between 1 us and 2 s");
+    return gemm_fp8_pts_impl(A, B, C, sa, sb, nullptr, 1, M, N, K, stream, wait_limit_ns, 0);
+}
 
 int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                             int64_t M, int64_t N, int64_t K, void* stream) {
@@ -707,6 +737,7 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
     p.sa = sa; p.sb = sb; p.bias = nullptr; p.C = (__nv_bfloat16*)C; p.gn = (int)gn;
     p.c_a = (const __nv_bfloat16*)c_a; p.c_b = (const __nv_bfloat16*)c_b;
+    p.wait_ns = kWaitLimitNs; p.skip_kblock = -1;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
     p.m_blks = (int)((M + BM - 1) / BM);

@@ -30,8 +30,9 @@ struct Mxfp4Params {
     int M, N, K, batch;
     int m_blks, n_blks;
     int katoms;                   // atoms per 128-row block in the scratch: K / 128 rounded up to even
-    int sfb_rblks;                // 128-row blocks of B's scales per batch in the scratch (incl. zero padding)
-    const uint8_t* sfa;           // re-laid-out scales of A: [batch, m_blks, katoms, 512]
+    int sfa_rblks;                // 128-row blocks of A's scales per batch (incl. padding)
+    int sfb_rblks;                // 128-row blocks of B's scales per batch (incl. padding)
+    const uint8_t* sfa;           // re-laid-out scales of A: [batch, sfa_rblks, katoms, 512]
     const uint8_t* sfb;           // re-laid-out scales of B: [batch, sfb_rblks, katoms, 512]
     __nv_bfloat16* C;
     const __nv_bfloat16* c_a;     // fused multiply-add epilogue C = c_a * (A B^T) + c_b, both [batch, M, N]; null = plain
@@ -152,7 +153,7 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int b = t / tiles_per_batch;
                 int mb, nb;
                 tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
-                const uint8_t* sfa_row = p.sfa + ((int64_t)b * p.m_blks + mb) * p.katoms * 512;
+                const uint8_t* sfa_row = p.sfa + ((int64_t)b * p.sfa_rblks + mb) * p.katoms * 512;
                 // first 128-row scale atom that the tile's B rows touch
                 const int atom0 = (nb * BN) >> 7;
                 const uint8_t* sfb_row = p.sfb + ((int64_t)b * p.sfb_rblks + atom0) * p.katoms * 512;
@@ -315,8 +316,7 @@ struct PairCfg {
 };
 
 struct Mxfp4PairParams {
-    Mxfp4Params g;                // m_blks counts 256-row blocks here
-    int sfa_rblks;                // 128-row blocks of A's scales per batch in the scratch (even)
+    Mxfp4Params g;                // m_blks counts 256-row blocks here; A's scale blocks are addressed as 2*mb + rank
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -384,7 +384,7 @@ gemm_mxfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 int mb, nb;
                 tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M / 2, mb, nb);
                 // scratch rows (256 bytes each) of this CTA's A-scale block and of the tile's two B-scale atoms
-                const int64_t sfa_row0 = (((int64_t)b * pp.sfa_rblks + 2 * mb + (int)rank) * p.katoms) * 2;
+                const int64_t sfa_row0 = (((int64_t)b * p.sfa_rblks + 2 * mb + (int)rank) * p.katoms) * 2;
                 const int atom0 = (nb * BN) >> 7;
                 const int64_t sfb_row0 = (((int64_t)b * p.sfb_rblks + atom0) * p.katoms) * 2;
                 for (int ks = 0; ks < kstages; ++ks) {
@@ -513,8 +513,25 @@ gemm_mxfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
 }
 
-int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, const void* sfb, const void* c_a, const void* c_b,
-                    int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+// Rows of 128-row scale blocks that the tensor-core layout of an operand with R rows holds per
+// batch: every block a kernel variant may address (CTA pairs address A's blocks as 2*mb + rank;
+// 192-wide tiles stage up to two atoms past the last one).
+inline int sf_tc_rblks(int64_t R) { return 2 * (int)((R + 255) / 256) + 2; }
+inline int sf_tc_katoms(int64_t K) { return ((int)(K / 128) + 1) & ~1; }
+
+int launch_sf_relayout(const void* src, void* dst, int64_t batch, int64_t R, int64_t K, cudaStream_t st) {
+    const int katoms_src = (int)(K / 128), katoms = sf_tc_katoms(K), rblks = sf_tc_rblks(R);
+    HKB_REQUIRE(rblks <= 65535 && batch <= 65535, HKB_ERR_BAD_SHAPE, "mxfp4 scale layout: too many row blocks");
+    dim3 g((unsigned)((katoms + 31) / 32), (unsigned)rblks, (unsigned)batch);
+    sf_relayout_kernel<<<g, 256, 0, st>>>((const uint8_t*)src, (uint8_t*)dst, (int)R, katoms_src, katoms, rblks);
+    return check_launch("sf_relayout_kernel");
+}
+
+// sfa_tc / sfb_tc: the scale pointer already is in the tensor-core layout (hkb_mxfp4_sf_to_tc or
+// hkb_quant_mxfp4_tc); otherwise it is row-major [batch, rows, K/32] and is re-laid-out into
+// per-(device, stream) scratch first.
+int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, const void* sfb, bool sfa_tc, bool sfb_tc,
+                    const void* c_a, const void* c_b, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
     HKB_REQUIRE(A && B && C && sfa && sfb, HKB_ERR_BAD_ARG, "gemm_mxfp4: null pointer");
     HKB_REQUIRE(batch >= 1 && M >= 1 && N >= 1 && K >= 1, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: empty problem");
     HKB_REQUIRE(K % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: K=%lld must be a multiple of 128", (long long)K);
@@ -522,6 +539,8 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
     HKB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) && batch < 65536, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: dimension too large");
     HKB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && ((uintptr_t)sfa & 3) == 0 && ((uintptr_t)sfb & 3) == 0,
                 HKB_ERR_BAD_ALIGN, "gemm_mxfp4: A, B, C must be 16-byte and the scale arrays 4-byte aligned");
+    HKB_REQUIRE((!sfa_tc || aligned16(sfa)) && (!sfb_tc || aligned16(sfb)), HKB_ERR_BAD_ALIGN,
+                "gemm_mxfp4: scale factors in the tensor-core layout must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     Mxfp4Params p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
@@ -532,10 +551,9 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
     const bool wide = (int64_t)p.m_blks * ((N + 191) / 192) * batch >= 2LL * sms;
     const int bn = wide ? 192 : 128;
     p.n_blks = (int)((N + bn - 1) / bn);
-    const int n_atoms = (int)((N + 127) / 128);
-    p.sfb_rblks = n_atoms + (wide ? 2 : 0);          // wide tiles may stage up to two atoms past the last one
-    const int katoms_src = (int)(K / 128);
-    p.katoms = (katoms_src + 1) & ~1;
+    p.sfa_rblks = sf_tc_rblks(M);
+    p.sfb_rblks = sf_tc_rblks(N);
+    p.katoms = sf_tc_katoms(K);
     p.C = (__nv_bfloat16*)C;
     p.c_a = (const __nv_bfloat16*)c_a;
     p.c_b = (const __nv_bfloat16*)c_b;
@@ -546,23 +564,25 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
     static const bool pairs_on = [] { const char* v = getenv("HKB_MXFP4_PAIRS"); return !(v && v[0] == '0'); }();
     const int64_t pair_tiles = ((M + 255) / 256) * ((N + 191) / 192) * batch;
     const bool pair = pairs_on && wide && M > 128 && pair_tiles >= sms / 2 && sms >= 2;
-    const int sfa_rblks = pair ? 2 * (int)((M + 255) / 256) : p.m_blks;      // pairs address A's scale blocks as 2*mb + rank
 
-    // scale re-layout into library-owned scratch (grown on demand, reused across calls)
-    void *sfa_sw = nullptr, *sfb_sw = nullptr;
-    const size_t sfa_bytes = (size_t)batch * sfa_rblks * p.katoms * 512;
+    const size_t sfa_bytes = (size_t)batch * p.sfa_rblks * p.katoms * 512;
     const size_t sfb_bytes = (size_t)batch * p.sfb_rblks * p.katoms * 512;
-    rc = scratch_get(SCRATCH_SFA, sfa_bytes, &sfa_sw);
-    if (rc != HKB_OK) return rc;
-    rc = scratch_get(SCRATCH_SFB, sfb_bytes, &sfb_sw);
-    if (rc != HKB_OK) return rc;
-    {
-        dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)sfa_rblks, (unsigned)batch);
-        sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)sfa, (uint8_t*)sfa_sw, (int)M, katoms_src, p.katoms, sfa_rblks);
-        dim3 gb((unsigned)((p.katoms + 31) / 32), (unsigned)p.sfb_rblks, (unsigned)batch);
-        sf_relayout_kernel<<<gb, 256, 0, st>>>((const uint8_t*)sfb, (uint8_t*)sfb_sw, (int)N, katoms_src, p.katoms, p.sfb_rblks);
-        rc = check_launch("sf_relayout_kernel");
+    const void *sfa_sw = sfa, *sfb_sw = sfb;
+    if (!sfa_tc) {
+        void* buf = nullptr;
+        rc = scratch_get(SCRATCH_SFA, st, sfa_bytes, &buf);
         if (rc != HKB_OK) return rc;
+        rc = launch_sf_relayout(sfa, buf, batch, M, K, st);
+        if (rc != HKB_OK) return rc;
+        sfa_sw = buf;
+    }
+    if (!sfb_tc) {
+        void* buf = nullptr;
+        rc = scratch_get(SCRATCH_SFB, st, sfb_bytes, &buf);
+        if (rc != HKB_OK) return rc;
+        rc = launch_sf_relayout(sfb, buf, batch, N, K, st);
+        if (rc != HKB_OK) return rc;
+        sfb_sw = buf;
     }
     p.sfa = (const uint8_t*)sfa_sw;
     p.sfb = (const uint8_t*)sfb_sw;
@@ -574,7 +594,6 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
         Mxfp4PairParams pp{};
         pp.g = p;
         pp.g.m_blks = (int)((M + 255) / 256);
-        pp.sfa_rblks = sfa_rblks;
         CUtensorMap tmSfa, tmSfb;
         rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, PairCfg::BN / 2);
         if (rc != HKB_OK) return rc;
@@ -600,6 +619,7 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
         cfg.numAttrs = 1;
         e = cudaLaunchKernelEx(&cfg, gemm_mxfp4_pair_kernel, tmA, tmB, tmSfa, tmSfb, pp);
         HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "launch of gemm_mxfp4_pair_kernel failed: %s", cudaGetErrorString(e));
+        note_kernel("gemm_mxfp4_pair_kernel<256x192>");
         return check_launch("gemm_mxfp4_pair_kernel");
     }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)batch, (uint32_t)bn);
@@ -610,10 +630,12 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
         const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<192>::kDynamic);
         HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
         gemm_mxfp4_kernel<192><<<grid, 192, Cfg<192>::kDynamic, st>>>(tmA, tmB, p);
+        note_kernel("gemm_mxfp4_kernel<192>");
     } else {
         const cudaError_t e = cudaFuncSetAttribute(gemm_mxfp4_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::kDynamic);
         HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
         gemm_mxfp4_kernel<128><<<grid, 192, Cfg<128>::kDynamic, st>>>(tmA, tmB, p);
+        note_kernel("gemm_mxfp4_kernel<128>");
     }
     return check_launch("gemm_mxfp4_kernel");
 }
@@ -623,7 +645,27 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
 
 extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                               int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
-    return hkb::gemm_mxfp4_impl(A, B, C, sfa, sfb, nullptr, nullptr, batch, M, N, K, stream);
+    return hkb::gemm_mxfp4_impl(A, B, C, sfa, sfb, false, false, nullptr, nullptr, batch, M, N, K, stream);
+}
+
+extern "C" int64_t hkb_mxfp4_sf_tc_bytes(int64_t batch, int64_t rows, int64_t K) {
+    if (batch < 1 || rows < 1 || K < 128 || K % 128) return 0;
+    return batch * (int64_t)hkb::sf_tc_rblks(rows) * hkb::sf_tc_katoms(K) * 512;
+}
+
+extern "C" int hkb_mxfp4_sf_to_tc(const void* sf, void* sf_tc, int64_t batch, int64_t rows, int64_t K, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(sf && sf_tc, HKB_ERR_BAD_ARG, "mxfp4_sf_to_tc: null pointer");
+    HKB_REQUIRE(batch >= 1 && rows >= 1 && K >= 128 && K % 128 == 0 && rows < (1LL << 31) && K < (1LL << 31), HKB_ERR_BAD_SHAPE,
+                "mxfp4_sf_to_tc: need batch, rows >= 1 and K a positive multiple of 128");
+    HKB_REQUIRE(((uintptr_t)sf & 3) == 0 && aligned16(sf_tc), HKB_ERR_BAD_ALIGN,
+                "mxfp4_sf_to_tc: sf must be 4-byte and sf_tc 16-byte aligned");
+    return launch_sf_relayout(sf, sf_tc, batch, rows, K, (cudaStream_t)stream);
+}
+
+extern "C" int hkb_gemm_mxfp4_tc(const void* A, const void* B, void* C, const void* sfa, int sfa_is_tc, const void* sfb,
+                                 int sfb_is_tc, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+    return hkb::gemm_mxfp4_impl(A, B, C, sfa, sfb, sfa_is_tc != 0, sfb_is_tc != 0, nullptr, nullptr, batch, M, N, K, stream);
 }
 
 extern "C" int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
@@ -631,7 +673,7 @@ extern "C" int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, con
     using namespace hkb;
     HKB_REQUIRE(c_a && c_b, HKB_ERR_BAD_ARG, "gemm_mxfp4_mul_add: null c_a / c_b");
     HKB_REQUIRE(aligned16(c_a) && aligned16(c_b), HKB_ERR_BAD_ALIGN, "gemm_mxfp4_mul_add: c_a and c_b must be 16-byte aligned");
-    return gemm_mxfp4_impl(A, B, C, sfa, sfb, c_a, c_b, 1, M, N, K, stream);
+    return gemm_mxfp4_impl(A, B, C, sfa, sfb, false, false, c_a, c_b, 1, M, N, K, stream);
 }
 
 
@@ -657,13 +699,17 @@ extern "C" int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, con
 //     overlap on the GPU (different streams, or different host threads) race on the array; run
 //     them in one stream or order them with events.
 //   * Bounded-wait timeouts of this variant are recorded in a word of the same image
-//     (g_static_status), not in the word hkb_check_status() reads.
+//     (g_static_status); hkb_check_status() reads and clears it together with the ordinary one,
+//     without allocating.
+//   * It always runs the one-CTA kernel on 128 x 128 tiles (the 192-wide and CTA-pair kernels of
+//     hkb_gemm_mxfp4 address padded scale blocks that would cut the size limit further), so on
+//     large problems it is the slower of the two entry points.
 namespace hkb {
 namespace {
 
 constexpr size_t kStaticSfBytes = (size_t)8 << 20;
 static __device__ __align__(256) uint8_t g_static_sf[kStaticSfBytes];
-static __device__ __align__(256) uint32_t g_static_status[64];
+static __device__ __align__(256) uint32_t g_static_status[1];
 
 struct StaticSlot {
     uint8_t* sf = nullptr;       // device address of g_static_sf on this device
@@ -694,6 +740,14 @@ int static_addresses(StaticSlot* out) {
 }
 
 }  // namespace
+
+uint32_t* static_status_peek() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    return g_static_slot[dev].status;
+}
+
 }  // namespace hkb
 
 extern "C" int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
@@ -711,6 +765,7 @@ extern "C" int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, cons
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.m_blks = (int)((M + BM - 1) / BM);
     p.n_blks = (int)((N + 127) / 128);
+    p.sfa_rblks = p.m_blks;
     p.sfb_rblks = p.n_blks;
     const int katoms_src = (int)(K / 128);
     p.katoms = (katoms_src + 1) & ~1;
@@ -746,5 +801,6 @@ extern "C" int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, cons
     const int sms = sm_count();
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
     gemm_mxfp4_kernel<128><<<tiles < sms ? tiles : sms, 192, Cfg<128>::kDynamic, st>>>(tmA, tmB, p);
+    note_kernel("gemm_mxfp4_kernel<128> (static scratch)");
     return check_launch("gemm_mxfp4_kernel");
 }

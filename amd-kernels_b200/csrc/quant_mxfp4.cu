@@ -85,10 +85,24 @@ __device__ __forceinline__ uint32_t encode8_bf16(const uint4& v, float inv) {
 
 // Two adjacent lanes own one 32-element block: lane (b, h) holds elements [16h, 16h+16) of
 // block b.  A warp covers 16 blocks per iteration, a thread keeps ITER 32-byte chunks in flight.
-template <int MODE, int ITER>
+// Where the four scale bytes of K atom `ka` of row `r` live in the tensor-core layout (see
+// gemm_mxfp4.cu): atoms of 512 bytes, byte (r%32)*16 + ((r%128)/32)*4 + j inside an atom, atoms
+// of a 128-row block consecutive along K (katoms_pad of them per block).
+struct SfTc {
+    uint8_t* base;        // null: no tensor-core-layout output
+    uint32_t kgroups;     // D / 128: K atoms per row
+    uint32_t katoms_pad;  // kgroups rounded up to even
+};
+__device__ __forceinline__ uint32_t* sf_tc_word(const SfTc& tc, uint32_t r, uint32_t ka) {
+    return reinterpret_cast<uint32_t*>(tc.base + ((size_t)(r >> 7) * tc.katoms_pad + ka) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4);
+}
+
+// TC: also (or, with scales == null, only) write the scale bytes in the tensor-core layout; rows
+// are then made of whole 128-element groups and total_blocks < 2^31.
+template <int MODE, int ITER, bool TC = false>
 __global__ void __launch_bounds__(256)
 quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ codes,
-                   uint8_t* __restrict__ scales, int64_t total_blocks) {
+                   uint8_t* __restrict__ scales, int64_t total_blocks, const SfTc tc = SfTc{}) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = lane & 1;
     const int64_t b0 = ((int64_t)blockIdx.x * 8 + warp) * (16 * ITER) + (lane >> 1);
@@ -115,7 +129,15 @@ quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ co
         const uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, l8) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 2) << 8) |
                               (__shfl_sync(0xFFFFFFFFu, sb, l8 + 4) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 6) << 24);
         const int64_t b4 = b & ~(int64_t)3;
-        if (b4 + 4 <= total_blocks) {
+        if constexpr (TC) {
+            if (b < total_blocks && (lane & 7) == 0) {       // D % 128 == 0: the four blocks are one K atom of one row
+                if (scales) *reinterpret_cast<uint32_t*>(scales + b) = word;
+                const uint32_t g = (uint32_t)b >> 2;
+                const uint32_t r = g / tc.kgroups, ka = g - r * tc.kgroups;
+                *sf_tc_word(tc, r, ka) = word;
+                if (ka + 1 == tc.kgroups && tc.katoms_pad != tc.kgroups) *sf_tc_word(tc, r, ka + 1) = 0u;   // padding atom of an odd D/128
+            }
+        } else if (b4 + 4 <= total_blocks) {
             if ((lane & 7) == 0) *reinterpret_cast<uint32_t*>(scales + b) = word;
         } else if (b < total_blocks && h == 0) {
             scales[b] = (uint8_t)sb;
@@ -133,7 +155,8 @@ quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ co
 template <int NW, int TPR, int MODE>
 __global__ void __launch_bounds__(256, NW <= 4 ? 3 : 2)
 rmsnorm_quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int64_t M, int nwide, float eps) {
+                           uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int64_t M, int nwide, float eps,
+                           const SfTc tc) {
     constexpr int RPB = 256 / TPR;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -217,61 +240,100 @@ rmsnorm_quant_mxfp4_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
         const uint32_t word = __shfl_sync(0xFFFFFFFFu, sb, l8) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 2) << 8) |
                               (__shfl_sync(0xFFFFFFFFu, sb, l8 + 4) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, l8 + 6) << 24);
         if (ok) {
-            if (words) { if ((t & 7) == 0) *reinterpret_cast<uint32_t*>(sr + (c >> 1)) = word; }
+            if (tc.base) {          // rows are whole 128-element groups here
+                if ((t & 7) == 0) {
+                    const uint32_t ka = (uint32_t)c >> 3;
+                    if (scales) *reinterpret_cast<uint32_t*>(sr + (c >> 1)) = word;
+                    *sf_tc_word(tc, (uint32_t)row, ka) = word;
+                    if (ka + 1 == tc.kgroups && tc.katoms_pad != tc.kgroups) *sf_tc_word(tc, (uint32_t)row, ka + 1) = 0u;
+                }
+            } else if (words) { if ((t & 7) == 0) *reinterpret_cast<uint32_t*>(sr + (c >> 1)) = word; }
             else if ((t & 1) == 0) sr[c >> 1] = (uint8_t)sb;
         }
     }
 }
 
 template <int TPR, int MODE>
-int launch_rms_mxfp4(int n, const void* x, const void* w, void* codes, void* scales, int64_t M, int nwide, float eps, cudaStream_t st) {
+int launch_rms_mxfp4(int n, const void* x, const void* w, void* codes, void* scales, int64_t M, int nwide, float eps, const SfTc& tc, cudaStream_t st) {
     constexpr int RPB = 256 / TPR;
     const unsigned grid = (unsigned)((M + RPB - 1) / RPB);
-#define HKB_RMS(NWV) rmsnorm_quant_mxfp4_kernel<NWV, TPR, MODE><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)codes, (uint8_t*)scales, M, nwide, eps)
+#define HKB_RMS(NWV) rmsnorm_quant_mxfp4_kernel<NWV, TPR, MODE><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (uint8_t*)codes, (uint8_t*)scales, M, nwide, eps, tc)
     if (n <= 1) HKB_RMS(1); else if (n <= 2) HKB_RMS(2); else if (n <= 4) HKB_RMS(4); else HKB_RMS(8);
 #undef HKB_RMS
     return check_launch("rmsnorm_quant_mxfp4_kernel");
 }
 
 template <int MODE>
-int dispatch_rms_mxfp4(const void* x, const void* w, void* codes, void* scales, int64_t M, int nwide, float eps, cudaStream_t st) {
+int dispatch_rms_mxfp4(const void* x, const void* w, void* codes, void* scales, int64_t M, int nwide, float eps, const SfTc& tc, cudaStream_t st) {
     int tpr = 32;
     while (tpr < 256 && tpr * 4 < nwide) tpr *= 2;
     const int n = (nwide + tpr - 1) / tpr;
     switch (tpr) {
-        case 32: return launch_rms_mxfp4<32, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
-        case 64: return launch_rms_mxfp4<64, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
-        case 128: return launch_rms_mxfp4<128, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
-        default: return launch_rms_mxfp4<256, MODE>(n, x, w, codes, scales, M, nwide, eps, st);
+        case 32: return launch_rms_mxfp4<32, MODE>(n, x, w, codes, scales, M, nwide, eps, tc, st);
+        case 64: return launch_rms_mxfp4<64, MODE>(n, x, w, codes, scales, M, nwide, eps, tc, st);
+        case 128: return launch_rms_mxfp4<128, MODE>(n, x, w, codes, scales, M, nwide, eps, tc, st);
+        default: return launch_rms_mxfp4<256, MODE>(n, x, w, codes, scales, M, nwide, eps, tc, st);
     }
 }
 
 }  // namespace
 }  // namespace hkb
 
-extern "C" int hkb_quant_mxfp4(const void* x, const void* w, void* codes, void* scales,
-                               int64_t M, int64_t D, float eps, int mode, void* stream) {
-    using namespace hkb;
-    HKB_REQUIRE(x && codes && scales, HKB_ERR_BAD_ARG, "quant_mxfp4: null pointer");
+namespace hkb {
+namespace {
+int quant_mxfp4_impl(const void* x, const void* w, void* codes, void* scales, void* sf_tc,
+                     int64_t M, int64_t D, float eps, int mode, void* stream) {
+    HKB_REQUIRE(x && codes && (scales || sf_tc), HKB_ERR_BAD_ARG, "quant_mxfp4: null pointer");
     HKB_REQUIRE(mode == HKB_MXFP4_MODE_DOC || mode == HKB_MXFP4_MODE_KERNEL, HKB_ERR_BAD_ARG, "quant_mxfp4: unknown mode %d", mode);
     HKB_REQUIRE(M >= 0 && D > 0 && D % 32 == 0, HKB_ERR_BAD_SHAPE, "quant_mxfp4: need D %% 32 == 0, got M=%lld D=%lld", (long long)M, (long long)D);
     HKB_REQUIRE(aligned32(x) && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)scales & 3) == 0 && (!w || aligned16(w)),
                 HKB_ERR_BAD_ALIGN, "quant_mxfp4: x must be 32-byte, w 16-byte, codes 8-byte, scales 4-byte aligned");
+    SfTc tc{};
+    if (sf_tc) {
+        HKB_REQUIRE(D % 128 == 0, HKB_ERR_BAD_SHAPE, "quant_mxfp4_tc: D=%lld must be a multiple of 128", (long long)D);
+        HKB_REQUIRE(M * (D / 32) < (1LL << 31), HKB_ERR_BAD_SHAPE, "quant_mxfp4_tc: tensor too large");
+        HKB_REQUIRE(aligned16(sf_tc), HKB_ERR_BAD_ALIGN, "quant_mxfp4_tc: sf_tc must be 16-byte aligned");
+        tc.base = (uint8_t*)sf_tc;
+        tc.kgroups = (uint32_t)(D / 128);
+        tc.katoms_pad = (tc.kgroups + 1) & ~1u;
+    }
     if (M == 0) return HKB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (w) {
         HKB_REQUIRE(D <= 32768 && M <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_mxfp4 with RMSNorm: D must be <= 32768");
         const int nwide = (int)(D / 16);
-        if (mode == HKB_MXFP4_MODE_KERNEL) return dispatch_rms_mxfp4<HKB_MXFP4_MODE_KERNEL>(x, w, codes, scales, M, nwide, eps, st);
-        return dispatch_rms_mxfp4<HKB_MXFP4_MODE_DOC>(x, w, codes, scales, M, nwide, eps, st);
+        if (mode == HKB_MXFP4_MODE_KERNEL) return dispatch_rms_mxfp4<HKB_MXFP4_MODE_KERNEL>(x, w, codes, scales, M, nwide, eps, tc, st);
+        return dispatch_rms_mxfp4<HKB_MXFP4_MODE_DOC>(x, w, codes, scales, M, nwide, eps, tc, st);
     }
     constexpr int ITER = 4;
     const int64_t blocks = M * (D / 32);
     const int64_t grid = (blocks + 128 * ITER - 1) / (128 * ITER);
     HKB_REQUIRE(grid <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "quant_mxfp4: tensor too large");
-    if (mode == HKB_MXFP4_MODE_KERNEL)
-        quant_mxfp4_kernel<HKB_MXFP4_MODE_KERNEL, ITER><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, blocks);
+    const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+    if (sf_tc) {
+        if (mode == HKB_MXFP4_MODE_KERNEL)
+            quant_mxfp4_kernel<HKB_MXFP4_MODE_KERNEL, ITER, true><<<(unsigned)grid, 256, 0, st>>>(xp, (uint8_t*)codes, (uint8_t*)scales, blocks, tc);
+        else
+            quant_mxfp4_kernel<HKB_MXFP4_MODE_DOC, ITER, true><<<(unsigned)grid, 256, 0, st>>>(xp, (uint8_t*)codes, (uint8_t*)scales, blocks, tc);
+    } else if (mode == HKB_MXFP4_MODE_KERNEL)
+        quant_mxfp4_kernel<HKB_MXFP4_MODE_KERNEL, ITER><<<(unsigned)grid, 256, 0, st>>>(xp, (uint8_t*)codes, (uint8_t*)scales, blocks);
     else
-        quant_mxfp4_kernel<HKB_MXFP4_MODE_DOC, ITER><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)x, (uint8_t*)codes, (uint8_t*)scales, blocks);
+        quant_mxfp4_kernel<HKB_MXFP4_MODE_DOC, ITER><<<(unsigned)grid, 256, 0, st>>>(xp, (uint8_t*)codes, (uint8_t*)scales, blocks);
     return check_launch("quant_mxfp4_kernel");
+}
+}  // namespace
+}  // namespace hkb
+
+extern "C" int hkb_quant_mxfp4(const void* x, const void* w, void* codes, void* scales,
+                               int64_t M, int64_t D, float eps, int mode, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(scales, HKB_ERR_BAD_ARG, "quant_mxfp4: null pointer");
+    return quant_mxfp4_impl(x, w, codes, scales, nullptr, M, D, eps, mode, stream);
+}
+
+extern "C" int hkb_quant_mxfp4_tc(const void* x, const void* w, void* codes, void* scales, void* sf_tc,
+                                  int64_t M, int64_t D, float eps, int mode, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(sf_tc, HKB_ERR_BAD_ARG, "quant_mxfp4_tc: null sf_tc");
+    return quant_mxfp4_impl(x, w, codes, scales, sf_tc, M, D, eps, mode, stream);
 }

@@ -20,10 +20,17 @@ int set_error(int code, const char* fmt, ...) {
 
 namespace {
 constexpr int kMaxDev = 64;
+struct StreamScratch {
+    cudaStream_t stream = nullptr;
+    bool used = false;
+    uint64_t last_use = 0;
+    void* block[SCRATCH_SLOTS] = {};
+    size_t bytes[SCRATCH_SLOTS] = {};
+};
 struct DeviceState {
     int sms = 0;
-    void* scratch[SCRATCH_SLOTS] = {};
-    size_t scratch_bytes[SCRATCH_SLOTS] = {};
+    StreamScratch scratch[kScratchStreams];
+    uint64_t clock = 0;
     uint32_t* status = nullptr;
 };
 DeviceState g_dev[kMaxDev];
@@ -48,23 +55,44 @@ int sm_count() {
     return g_dev[dev].sms;
 }
 
-int scratch_get(ScratchSlot slot, size_t bytes, void** out) {
+int scratch_get(ScratchSlot slot, cudaStream_t stream, size_t bytes, void** out) {
     int dev = 0;
     int rc = current_device(&dev);
     if (rc != HKB_OK) return rc;
     std::lock_guard<std::mutex> lk(g_mu);
     DeviceState& d = g_dev[dev];
-    if (d.scratch_bytes[slot] < bytes) {
+    // the entry of this stream, else a free one, else the least recently used one
+    StreamScratch* e = nullptr;
+    for (auto& c : d.scratch)
+        if (c.used && c.stream == stream) { e = &c; break; }
+    if (!e)
+        for (auto& c : d.scratch)
+            if (!c.used) { e = &c; break; }
+    if (!e) {
+        e = &d.scratch[0];
+        for (auto& c : d.scratch)
+            if (c.last_use < e->last_use) e = &c;
+        // Another stream's launches may still read these blocks: cudaFree waits for the device.
+        for (int i = 0; i < SCRATCH_SLOTS; ++i) {
+            if (e->block[i]) HKB_CUDA(cudaFree(e->block[i]));
+            e->block[i] = nullptr;
+            e->bytes[i] = 0;
+        }
+    }
+    e->used = true;
+    e->stream = stream;
+    e->last_use = ++d.clock;
+    if (e->bytes[slot] < bytes) {
         // Growing frees the old block; earlier launches that still use it are ordered before
         // the free by the implicit synchronisation of cudaFree.
-        if (d.scratch[slot]) HKB_CUDA(cudaFree(d.scratch[slot]));
-        d.scratch[slot] = nullptr;
-        d.scratch_bytes[slot] = 0;
+        if (e->block[slot]) HKB_CUDA(cudaFree(e->block[slot]));
+        e->block[slot] = nullptr;
+        e->bytes[slot] = 0;
         size_t want = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
-        HKB_CUDA(cudaMalloc(&d.scratch[slot], want));
-        d.scratch_bytes[slot] = want;
+        HKB_CUDA(cudaMalloc(&e->block[slot], want));
+        e->bytes[slot] = want;
     }
-    *out = d.scratch[slot];
+    *out = e->block[slot];
     return HKB_OK;
 }
 
@@ -82,11 +110,16 @@ int status_word(uint32_t** out) {
     return HKB_OK;
 }
 
+static thread_local const char* g_last_kernel = "";
+void note_kernel(const char* name) { g_last_kernel = name; }
+
 }  // namespace hkb
 
 extern "C" {
 
-int hkb_version(void) { return 100; }
+int hkb_version(void) { return 200; }
+
+const char* hkb_last_kernel(void) { return hkb::g_last_kernel; }
 
 const char* hkb_last_error(void) { return hkb::g_err.c_str(); }
 
@@ -103,13 +136,13 @@ int hkb_release(void) {
     for (int d = 0; d < ndev && d < kMaxDev; ++d) {
         DeviceState& s = g_dev[d];
         bool any = s.status != nullptr;
-        for (int i = 0; i < SCRATCH_SLOTS; ++i) any = any || s.scratch[i];
+        for (auto& c : s.scratch) any = any || c.used;
         if (!any) continue;
         HKB_CUDA(cudaSetDevice(d));
-        for (int i = 0; i < SCRATCH_SLOTS; ++i) {
-            if (s.scratch[i]) HKB_CUDA(cudaFree(s.scratch[i]));
-            s.scratch[i] = nullptr;
-            s.scratch_bytes[i] = 0;
+        for (auto& c : s.scratch) {
+            for (int i = 0; i < SCRATCH_SLOTS; ++i)
+                if (c.block[i]) HKB_CUDA(cudaFree(c.block[i]));
+            c = StreamScratch{};
         }
         if (s.status) HKB_CUDA(cudaFree(s.status));
         s.status = nullptr;
@@ -120,15 +153,28 @@ int hkb_release(void) {
 
 int hkb_check_status(void* stream) {
     using namespace hkb;
-    uint32_t* w = nullptr;
-    int rc = status_word(&w);
+    // Two words can hold a failure: the allocated one of the ordinary entry points and the one built
+    // into the library image that the allocation-free entry point uses.  Neither is created here:
+    // a word that no launch has used yet cannot hold anything.
+    int dev = 0;
+    int rc = current_device(&dev);
     if (rc != HKB_OK) return rc;
-    uint32_t host = 0;
-    HKB_CUDA(cudaMemcpyAsync(&host, w, sizeof host, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-    HKB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    if (host != 0) {
-        cudaMemsetAsync(w, 0, sizeof host, (cudaStream_t)stream);
-        return set_error(HKB_ERR_TIMEOUT, "a kernel abandoned a bounded wait (status 0x%08x)", host);
+    uint32_t* words[2];
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        words[0] = g_dev[dev].status;
+    }
+    words[1] = static_status_peek();
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t host[2] = {0, 0};
+    for (int i = 0; i < 2; ++i)
+        if (words[i]) HKB_CUDA(cudaMemcpyAsync(&host[i], words[i], sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    HKB_CUDA(cudaStreamSynchronize(st));
+    if (host[0] | host[1]) {
+        for (int i = 0; i < 2; ++i)
+            if (host[i]) cudaMemsetAsync(words[i], 0, sizeof(uint32_t), st);
+        return set_error(HKB_ERR_TIMEOUT, "a kernel abandoned a bounded wait (status 0x%08x%s)", host[0] | host[1],
+                         host[1] ? ", allocation-free entry point" : "");
     }
     return HKB_OK;
 }

@@ -194,6 +194,30 @@ int mxfp4_mode(const py::object& mode) {
     check(hkb_quant_mxfp4(x.ptr, w.none ? nullptr : w.ptr, q.ptr, s.ptr, M, D, eps, m, L.stream));
 }
 
+// Not in the reference: the same quantizer writing its scales (also, or only when scales is None)
+// in the layout the MXFP4 GEMM's tensor-core path reads, so that the GEMM needs no re-layout pass.
+[[maybe_unused]] void fused_rmsnorm_mxfp4_quant_tc_fwd(py::object input, py::object weight, py::object output,
+                                                       py::object scales, py::object sf_tc, float eps, py::object mode) {
+    TView x = view(input, "input"), w = view(weight, "weight", true), q = view(output, "output"), s = view(scales, "scales", true),
+          tc = view(sf_tc, "sf_tc");
+    want_dtype(x, "input", {"bfloat16"});
+    if (!w.none) want_dtype(w, "weight", {"bfloat16"});
+    want_dtype(q, "output", {"uint8", "float4_e2m1fn_x2"});
+    if (!s.none) want_dtype(s, "scales", {"uint8", "float8_e8m0fnu"});
+    want_dtype(tc, "sf_tc", {"uint8", "float8_e8m0fnu"});
+    if (x.rank() != 2) fail("input must be [M, D]");
+    const int64_t M = x.dim(0), D = x.dim(1);
+    if (D % 128 != 0) fail("Unsupported D=" + std::to_string(D) + ": D must be a multiple of 128");
+    if (!w.none && w.numel != D) fail("weight must have D elements");
+    if (q.numel != M * D / 2) fail("output must have M*D/2 bytes");
+    if (!s.none && s.numel != M * (D / 32)) fail("scales must have M*(D/32) bytes");
+    if (tc.numel < hkb_mxfp4_sf_tc_bytes(1, M, D)) fail("sf_tc must have sf_tc_bytes(1, M, D) bytes");
+    same_device({&x, &w, &q, &s, &tc});
+    const int m = mxfp4_mode(mode);
+    Launch L(x.device);
+    check(hkb_quant_mxfp4_tc(x.ptr, w.none ? nullptr : w.ptr, q.ptr, s.none ? nullptr : s.ptr, tc.ptr, M, D, eps, m, L.stream));
+}
+
 // ---- GEMMs ---------------------------------------------------------------------------------
 
 struct GemmDims { int64_t batch, M, N, K; };
@@ -328,6 +352,36 @@ void mxfp4(py::object A_, py::object B_, py::object C_, py::object sfa_, py::obj
 [[maybe_unused]] void dispatch_mxfp4(py::object A, py::object B, py::object C, py::object sfa, py::object sfb) {
     mxfp4(A, B, C, sfa, sfb, py::none(), py::none());
 }
+// Not in the reference: scale factors already in the tensor-core layout (see include/hkb200.h).
+[[maybe_unused]] int64_t mxfp4_sf_tc_bytes(int64_t batch, int64_t rows, int64_t K) { return hkb_mxfp4_sf_tc_bytes(batch, rows, K); }
+[[maybe_unused]] void mxfp4_sf_to_tc(py::object sf_, py::object tc_, int64_t K) {
+    TView sf = view(sf_, "scales"), tc = view(tc_, "sf_tc");
+    want_dtype(sf, "scales", {"uint8", "float8_e8m0fnu"});
+    want_dtype(tc, "sf_tc", {"uint8", "float8_e8m0fnu"});
+    if (sf.rank() < 2 || K % 128 || sf.dim(-1) != K / 32) fail("scales must be [.., rows, K/32] with K a multiple of 128");
+    const int64_t rows = sf.dim(-2), batch = sf.numel / (rows * sf.dim(-1));
+    if (tc.numel < hkb_mxfp4_sf_tc_bytes(batch, rows, K)) fail("sf_tc must have sf_tc_bytes(batch, rows, K) bytes");
+    same_device({&sf, &tc});
+    Launch L(sf.device);
+    check(hkb_mxfp4_sf_to_tc(sf.ptr, tc.ptr, batch, rows, K, L.stream));
+}
+[[maybe_unused]] void dispatch_mxfp4_tc(py::object A_, py::object B_, py::object C_, py::object sfa_, py::object sfb_,
+                                        bool a_is_tc, bool b_is_tc) {
+    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sfa = view(sfa_, "a_scales"), sfb = view(sfb_, "b_scales");
+    want_dtype(A, "A", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(B, "B", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(C, "C", {"bfloat16"});
+    want_dtype(sfa, "a_scales", {"uint8", "float8_e8m0fnu"});
+    want_dtype(sfb, "b_scales", {"uint8", "float8_e8m0fnu"});
+    GemmDims d = gemm_dims(A, B, C, 2, 1);
+    if (a_is_tc ? sfa.numel < hkb_mxfp4_sf_tc_bytes(d.batch, d.M, d.K) : sfa.numel != d.batch * d.M * (d.K / 32))
+        fail("a_scales must be [batch, M, K/32], or sf_tc_bytes(batch, M, K) bytes in the tensor-core layout");
+    if (b_is_tc ? sfb.numel < hkb_mxfp4_sf_tc_bytes(d.batch, d.N, d.K) : sfb.numel != d.batch * d.N * (d.K / 32))
+        fail("b_scales must be [batch, N, K/32], or sf_tc_bytes(batch, N, K) bytes in the tensor-core layout");
+    same_device({&A, &B, &C, &sfa, &sfb});
+    Launch L(A.device);
+    check(hkb_gemm_mxfp4_tc(A.ptr, B.ptr, C.ptr, sfa.ptr, a_is_tc ? 1 : 0, sfb.ptr, b_is_tc ? 1 : 0, d.batch, d.M, d.N, d.K, L.stream));
+}
 // fused_gemm_afp4wfp4_mul_add_tk.dispatch(a, b, c, a_scale, b_scale, c_a, c_b):
 // kernels/gemm-fused/fused_gemm_afp4wfp4_mul_add/kernel.cpp:182-191.  Packed e2m1 / e8m0 operands.
 [[maybe_unused]] void dispatch_mxfp4_mul_add(py::object A, py::object B, py::object C, py::object sfa, py::object sfb,
@@ -395,6 +449,8 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
     m.doc() = "MXFP4 (e2m1 + e8m0 per 32) quantizer with optional fused RMSNorm, sm_100a";
     m.def("fused_rmsnorm_mxfp4_quant_fwd", &fused_rmsnorm_mxfp4_quant_fwd, "input"_a, "weight"_a, "output"_a, "scales"_a,
           "eps"_a = 1e-6f, "mode"_a = py::none());
+    m.def("fused_rmsnorm_mxfp4_quant_tc_fwd", &fused_rmsnorm_mxfp4_quant_tc_fwd, "input"_a, "weight"_a, "output"_a, "scales"_a,
+          "sf_tc"_a, "eps"_a = 1e-6f, "mode"_a = py::none());
 #elif defined(HKB_SHIM_GEMM_A8W8)
     m.doc() = "FP8 GEMM with per-row / per-channel scales (argument order A, B, a_scale, b_scale, C), sm_100a tcgen05";
     m.def("dispatch", &dispatch_a8w8, "A"_a, "B"_a, "a_scale"_a, "b_scale"_a, "C"_a);
@@ -407,6 +463,9 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_GEMM_AFP4WFP4)
     m.doc() = "MXFP4 x MXFP4 GEMM (e2m1 codes, e8m0 scales per 32), sm_100a tcgen05 block-scaled MMA";
     m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());
+    m.def("sf_tc_bytes", &mxfp4_sf_tc_bytes, "batch"_a, "rows"_a, "K"_a);
+    m.def("sf_to_tc", &mxfp4_sf_to_tc, "scales"_a, "sf_tc"_a, "K"_a);
+    m.def("dispatch_tc", &dispatch_mxfp4_tc, "A"_a, "B"_a, "C"_a, "a_scales"_a, "b_scales"_a, "a_is_tc"_a, "b_is_tc"_a);
 #elif defined(HKB_SHIM_BATCHED_GEMM_A8W8)
     m.doc() = "batched FP8 GEMM with per-token / per-channel scales and optional bias, sm_100a tcgen05";
     m.def("dispatch", &dispatch_batched_a8w8, "A"_a, "B"_a, "a_scale"_a, "b_scale"_a, "C"_a, "bias"_a = py::none());
@@ -428,4 +487,5 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #error "unknown shim selector"
 #endif
     m.def("hkb_version", []() { return hkb_version(); });
+    m.def("hkb_last_kernel", []() { return std::string(hkb_last_kernel()); });
 }

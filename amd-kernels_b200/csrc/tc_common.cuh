@@ -70,11 +70,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: true when the phase completed; false after kWaitLimitNs or when another role
+// Bounded wait: true when the phase completed; false after limit_ns or when another role
 // already raised the CTA's abort flag.  On a timeout the error bit is recorded in the device
 // status word and the abort flag is set so that every role of the CTA winds down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t err_bit) {
+                                          uint32_t* status, uint32_t err_bit, uint64_t limit_ns = kWaitLimitNs) {
     // The clock is read only every 1024 polls, the first time after 1024 polls: a %globaltimer
     // read costs hundreds of cycles, and a wait that is about to succeed must not sit behind one
     // (roles that hand a buffer back and forth per K block wait on every hand-off).
@@ -86,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicOr(status, err_bit);
                 return false;

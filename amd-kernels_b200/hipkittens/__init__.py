@@ -127,6 +127,18 @@ def fused_rmsnorm_mxfp4_quant_fwd(*args, **kwargs):
     return _call("fused_mxfp4_quant_tk", "fused_rmsnorm_mxfp4_quant_fwd", *args, **kwargs)
 
 
+def fused_rmsnorm_mxfp4_quant_tc_fwd(*args, **kwargs):
+    """(input, weight_or_None, output u8 [M,D/2], scales_or_None, sf_tc, eps[, mode]) -- not in the
+    reference: also writes the scales in the MXFP4 GEMM's tensor-core layout (``sf_tc`` of
+    ``hk.gemm.afp4wfp4.sf_tc_bytes(1, M, D)`` bytes) so that ``dispatch_tc`` needs no re-layout."""
+    return _call("fused_mxfp4_quant_tk", "fused_rmsnorm_mxfp4_quant_tc_fwd", *args, **kwargs)
+
+
+def last_kernel():
+    """Name of the kernel variant the last GEMM call of this thread launched (tests, tuning)."""
+    return _call("quant_tk", "hkb_last_kernel")
+
+
 def weight_quant_128x128(*args, **kwargs):
     """(weight bf16 [N,K], output [N,K], scales f32 [K/128,N/128]) -- not in the reference;
     produces the block-scale GEMM's weight operand."""

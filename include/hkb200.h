@@ -35,11 +35,25 @@ typedef enum {
 /* ---- library ------------------------------------------------------------------------- */
 int hkb_version(void);
 const char* hkb_last_error(void);
-/* Frees the per-device workspace (scale re-layout scratch, split-K partials, status word). */
+/* Frees the per-device workspace (scale re-layout scratch, status word). */
 int hkb_release(void);
 /* Synchronises `stream` and returns HKB_ERR_TIMEOUT if any GEMM launched so far on the
- * current device abandoned a bounded wait (it then left its output incomplete). */
+ * current device abandoned a bounded wait (it then left its output incomplete); the failure is
+ * cleared by the call.  Covers every entry point, hkb_gemm_mxfp4_static included, and allocates
+ * nothing. */
 int hkb_check_status(void* stream);
+/* Name of the kernel variant that the calling thread's last GEMM call launched (tile width, scale
+ * scheme, CTA pairs), e.g. "gemm_fp8_kernel<256,pts,pair>".  For tests and tuning: the variant is
+ * chosen from the problem size and the SM count. */
+const char* hkb_last_kernel(void);
+/* Test hook for the bounded waits: hkb_gemm_fp8_pts (batch 1, no bias) whose producer leaves the
+ * first K block of its first tile unloaded and whose waits give up after wait_limit_ns instead of
+ * 2 s.  The kernel winds down by itself, frees its tensor memory and records the failure, which
+ * hkb_check_status() then reports as HKB_ERR_TIMEOUT; C is left incomplete.  The device stays
+ * usable.  No counterpart in the reference project. */
+int hkb_debug_gemm_fp8_wait_probe(const void* A, const void* B, void* C, const float* sa,
+                                  const float* sb, int64_t M, int64_t N, int64_t K,
+                                  uint64_t wait_limit_ns, void* stream);
 
 /* ---- quantizers ---------------------------------------------------------------------- */
 
@@ -83,7 +97,7 @@ int hkb_quant_mxfp4(const void* x, const void* w_or_null, void* codes, void* sca
 
 /* C[b] = bf16( (A[b] @ B[b]^T) * sa[b][m] * sb[b][n] + bias[b][n] ), e4m3fn operands.
  * batch >= 1; tensors of consecutive batches are contiguous; bias (bf16 [batch, N]) may be NULL.
- * K % 128 == 0, N % 8 == 0.  Replaces
+ * K % 128 == 0, N % 8 == 0; A, B, C, sb and bias 16-byte, sa 4-byte aligned.  Replaces
  *   gemm_a8w8_per_token_scale_tk.dispatch(A,B,C,a_scale,b_scale)
  *       kernels/gemm-basic/gemm_a8w8_per_token_scale/kernel.cpp:49-171
  *   gemm_a8w8_tk.dispatch(A,B,a_scale,b_scale,C)   kernels/gemm-basic/gemm_a8w8/kernel.cpp:46-175
@@ -112,13 +126,42 @@ int hkb_gemm_fp8_blockscale_mul_add(const void* A, const void* B, void* C, const
 
 /* C[b] = bf16( dq(A[b]) @ dq(B[b])^T ), dq(v)[i,k] = e2m1(v[i,k]) * 2^(s[i,k/32]-127).
  * A u8 [batch, M, K/2], B u8 [batch, N, K/2], sfa u8 [batch, M, K/32], sfb u8 [batch, N, K/32].
- * K % 128 == 0, N % 8 == 0.  Uses library-owned scratch for the scale re-layout.  Replaces
+ * K % 128 == 0, N % 8 == 0.  The scales are first re-laid-out for the tensor core into
+ * library-owned scratch that is kept per (device, stream): calls on different streams of a device
+ * may overlap on the GPU (up to 8 streams per device keep their own scratch; beyond that the least
+ * recently used stream's scratch is recycled behind a device-wide synchronisation).  A call that
+ * has to allocate or grow its stream's scratch calls cudaMalloc / cudaFree, so the first call of a
+ * size on a stream must come before any stream capture.  Replaces
  *   gemm_afp4wfp4_tk.dispatch           kernels/gemm-basic/gemm_afp4wfp4/kernel.cpp:1-12,48-159
  *   batched_gemm_afp4wfp4_tk.dispatch   kernels/gemm-batched/batched_gemm_afp4wfp4/kernel.cpp:3-7,52-168
  * (operand spec from those files' header comments; the reference kernels themselves take
  * host-dequantized bf16). */
 int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                    int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Scale factors in the layout the tensor core reads ("tc layout"): per batch and 128-row block,
+ * 512-byte atoms of 128 rows x 4 scale bytes (128 K elements), byte (r%32)*16 + (r/32)*4 + j for
+ * row r and scale j, atoms of a row block consecutive along K; row blocks and K atoms are padded
+ * (2*ceil(rows/256) + 2 blocks, an even number of atoms).  hkb_mxfp4_sf_tc_bytes gives the size of
+ * that array (0 for invalid arguments); hkb_mxfp4_sf_to_tc fills it from row-major e8m0
+ * [batch, rows, K/32] (sf 4-byte, sf_tc 16-byte aligned), padding included.  Weights are converted
+ * once and reused; activations can be quantized straight into this layout (hkb_quant_mxfp4_tc).
+ * hkb_gemm_mxfp4_tc is hkb_gemm_mxfp4 where each of sfa / sfb is either row-major (flag 0, re-laid
+ * out per call as above) or already in the tc layout (flag 1, used in place: no scratch, no extra
+ * launch).  With both flags set the call allocates nothing.  No counterpart in the reference
+ * project, whose FP4 kernels take host-dequantized operands. */
+int64_t hkb_mxfp4_sf_tc_bytes(int64_t batch, int64_t rows, int64_t K);
+int hkb_mxfp4_sf_to_tc(const void* sf, void* sf_tc, int64_t batch, int64_t rows, int64_t K,
+                       void* stream);
+int hkb_gemm_mxfp4_tc(const void* A, const void* B, void* C, const void* sfa, int sfa_is_tc,
+                      const void* sfb, int sfb_is_tc, int64_t batch, int64_t M, int64_t N,
+                      int64_t K, void* stream);
+/* hkb_quant_mxfp4 that also (or only: scales may be NULL) writes the scales in the tc layout for
+ * an [M, D] operand of batch 1 (sf_tc of hkb_mxfp4_sf_tc_bytes(1, M, D) bytes, 16-byte aligned).
+ * D % 128 == 0.  Every byte of the real rows' atoms is written, the padding atom of an odd D/128
+ * included; padding ROWS are left untouched (they only meet output rows that are never stored). */
+int hkb_quant_mxfp4_tc(const void* x, const void* w_or_null, void* codes, void* scales_or_null,
+                       void* sf_tc, int64_t M, int64_t D, float eps, int mode, void* stream);
 
 /* hkb_gemm_mxfp4 (batch 1) with the multiply-add epilogue fused in: C = bf16( c_a * gemm + c_b ),
  * c_a and c_b bf16 [M, N] (16-byte aligned).  Replaces
@@ -163,7 +206,9 @@ int hkb_moe_upcast_mxfp(void* out, const void* mx_scale, const void* mx_tensor, 
  * 32768 at K = 8192); beyond it HKB_ERR_BAD_SHAPE is returned and nothing is launched.  The first
  * call on each device resolves the array's device address: make it outside stream capture.  All
  * calls on a device share the array; calls that may overlap on the GPU race on it and must be
- * ordered by the caller.  Bounded-wait failures of this variant are not visible to hkb_check_status.
+ * ordered by the caller.  It always runs the one-CTA kernel on 128-wide tiles, so on large problems
+ * it is slower than hkb_gemm_mxfp4 (which picks 192-wide tiles and CTA pairs).  Bounded-wait
+ * failures are reported by hkb_check_status like those of every other entry point.
  * No counterpart in the reference project. */
 int hkb_gemm_mxfp4_static(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                           int64_t batch, int64_t M, int64_t N, int64_t K, void* stream);

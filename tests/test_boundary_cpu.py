@@ -73,6 +73,41 @@ def test_bad_shapes_and_alignment_are_rejected_before_any_cuda_call(lib):
     assert lib.hkb_gemm_fp8_pts(q, p, p, f, f, None, i64(1), i64(128), i64(128), i64(128), None) == -3
 
 
+def test_offset_scale_and_bias_pointers_are_an_alignment_error(lib):
+    """b_scale and bias are read with 16-byte vector loads by the per-token epilogues: an offset view
+    must come back as HKB_ERR_BAD_ALIGN before any device is looked for."""
+    buf = ctypes.create_string_buffer(4096 + 64)
+    base = (ctypes.addressof(buf) + 63) & ~63
+    p = ctypes.c_void_p(base)
+    f = ctypes.cast(p, ctypes.POINTER(ctypes.c_float))
+    f_off = ctypes.cast(ctypes.c_void_p(base + 4), ctypes.POINTER(ctypes.c_float))
+    args = (i64(1), i64(128), i64(128), i64(128), None)
+    assert lib.hkb_gemm_fp8_pts(p, p, p, f, f_off, None, *args) == -3
+    assert b"16-byte" in lib.hkb_last_error()
+    assert lib.hkb_gemm_fp8_pts(p, p, p, f, f, ctypes.c_void_p(base + 2), *args) == -3
+    assert lib.hkb_gemm_fp8_pts(p, p, p, ctypes.cast(ctypes.c_void_p(base + 2), ctypes.POINTER(ctypes.c_float)), f, None, *args) == -3
+    # tensor-core-layout scale factors
+    assert lib.hkb_mxfp4_sf_to_tc(p, ctypes.c_void_p(base + 4), i64(1), i64(128), i64(128), None) == -3
+    assert lib.hkb_gemm_mxfp4_tc(p, p, p, ctypes.c_void_p(base + 4), 1, p, 1, i64(1), i64(128), i64(128), i64(128), None) == -3
+
+
+def test_mxfp4_tensor_core_layout_size(lib):
+    lib.hkb_mxfp4_sf_tc_bytes.restype = ctypes.c_int64
+    # 2*ceil(rows/256)+2 row blocks, K/128 rounded up to even atoms of 512 bytes
+    assert lib.hkb_mxfp4_sf_tc_bytes(i64(1), i64(8192), i64(8192)) == (2 * 32 + 2) * 64 * 512
+    assert lib.hkb_mxfp4_sf_tc_bytes(i64(3), i64(100), i64(384)) == 3 * 4 * 4 * 512
+    assert lib.hkb_mxfp4_sf_tc_bytes(i64(1), i64(128), i64(100)) == 0
+    assert lib.hkb_mxfp4_sf_tc_bytes(i64(0), i64(128), i64(128)) == 0
+
+
+def test_wait_probe_validates_its_limit(lib):
+    buf = ctypes.create_string_buffer(4096 + 64)
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 63) & ~63)
+    f = ctypes.cast(p, ctypes.POINTER(ctypes.c_float))
+    assert lib.hkb_debug_gemm_fp8_wait_probe(p, p, p, f, f, i64(128), i64(128), i64(128), ctypes.c_uint64(10), None) == -1
+    assert lib.hkb_debug_gemm_fp8_wait_probe(p, p, p, f, f, i64(128), i64(128), i64(128), ctypes.c_uint64(10**10), None) == -1
+
+
 def test_empty_input_is_a_no_op(lib):
     buf = ctypes.create_string_buffer(256)
     p = ctypes.c_void_p((ctypes.addressof(buf) + 63) & ~63)

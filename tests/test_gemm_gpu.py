@@ -204,6 +204,150 @@ def test_gemm_per_token_skinny_with_bias(hk):
     _check(C[0], gemm.gemm_fp8_per_token(aq, bq, sa, sb, bias.float().numpy()[0]), "skinny bias")
 
 
+# ---- the per-token kernels that large problems dispatch to ------------------------------------
+# Which kernel runs is decided from the tile counts and the SM count (148 on B200): 256-wide tiles
+# when ceil(M/128) * ceil(N/256) * batch >= 2 * SMs, as CTA pairs on 256 x 256 tiles when M > 128 and
+# at least SMs / 2 such tiles exist; else 128-wide tiles when twice the SM count of those exist;
+# else 64-wide tiles.  Each case asserts the variant through hkb_last_kernel().
+
+def _sampled_rows_check(C, aq, bq, sa, sb, what, nrows=128, bias=None):
+    """Oracle on `nrows` sampled rows (all columns), plus every element against an fp32 product on the device."""
+    M = aq.shape[-2]
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(3))[:min(nrows, M)].sort().values
+    ref = gemm.gemm_fp8_per_token(aq[..., rows.numpy(), :], bq, sa[..., rows], sb, bias)
+    _check(C[..., rows.to(DEV), :], ref, what + " (sampled rows vs oracle)")
+    full = torch.matmul(_dev(aq, torch.float8_e4m3fn).float(), _dev(bq, torch.float8_e4m3fn).float().transpose(-1, -2))
+    full = full * _dev(sa).unsqueeze(-1) * _dev(sb).unsqueeze(-2)
+    if bias is not None:
+        full = full + _dev(torch.from_numpy(bias)).unsqueeze(-2)
+    _check(C, full.cpu().numpy(), what + " (all elements vs device fp32)")
+
+
+@pytest.mark.parametrize("shape,kernel", [
+    ((2432, 4864, 512), "gemm_fp8_kernel<256,pts,pair>"),     # last 256-row block half empty
+    ((2400, 4864, 512), "gemm_fp8_kernel<256,pts,pair>"),     # last 256-row block: 96 rows, all in the leader CTA
+    ((4096, 14336, 256), "gemm_fp8_kernel<256,pts,pair>"),    # config 2's M and N
+    ((2048, 4608, 256), "gemm_fp8_kernel<128,pts>"),
+    ((2048, 4616, 256), "gemm_fp8_kernel<128,pts>"),          # N % 128 != 0: ragged last tile
+    ((2048, 2048, 2048), "gemm_fp8_kernel<64,pts>"),
+])
+def test_gemm_per_token_large_variants(hk, shape, kernel):
+    M, N, K = shape
+    aq, bq, sa, sb = _fp8_operands(M, N, K, seed=21)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(_dev(aq), _dev(bq), C, _dev(sa), _dev(sb))
+    assert hk.last_kernel() == kernel
+    torch.cuda.synchronize()
+    _status_ok()
+    _sampled_rows_check(C, aq, bq, sa, sb, f"per-token {shape} {kernel}", nrows=256)
+
+
+_SUBPROCESS_CASE = r"""
+import json, os, sys
+import numpy as np, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "amd-kernels_b200"))
+sys.path.insert(0, os.path.join({root!r}, "tests"))
+import hipkittens as hk
+import test_gemm_gpu as T
+from oracle import gemm
+kind, M, N, K, batch = {case!r}
+if kind == "pts":
+    aq, bq, sa, sb = T._fp8_operands(M, N, K, seed=22)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=T.DEV)
+    hk.gemm.a8w8_per_token.dispatch(T._dev(aq), T._dev(bq), C, T._dev(sa), T._dev(sb))
+    name = hk.last_kernel()
+    torch.cuda.synchronize()
+    err = gemm.rel_err(C.float().cpu().numpy(), gemm.gemm_fp8_per_token(aq, bq, sa, sb))
+else:
+    ac, wc, asc, wsc = T._mxfp4_operands(M, N, K, batch=batch, seed=23)
+    C = torch.full((batch, M, N), float("nan"), dtype=torch.bfloat16, device=T.DEV)
+    hk.batched_gemm.afp4wfp4.dispatch(T._dev(ac), T._dev(wc), C, T._dev(asc), T._dev(wsc))
+    name = hk.last_kernel()
+    torch.cuda.synchronize()
+    err = max(gemm.rel_err(C[b].float().cpu().numpy(), gemm.gemm_mxfp4(ac[b], wc[b], asc[b], wsc[b])) for b in range(batch))
+print(json.dumps({{"kernel": name, "rel_err": float(err)}}))
+"""
+
+
+def _run_case_in_subprocess(case, env_extra):
+    """Kernel selection switches are read once per process, so variants that need one run in a child."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, **env_extra)
+    r = subprocess.run([sys.executable, "-c", _SUBPROCESS_CASE.format(root=root, case=case)], env=env, capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def test_gemm_per_token_256_wide_single_cta_kernel():
+    """The 256-wide one-CTA kernel is what large problems get when CTA pairs are switched off."""
+    out = _run_case_in_subprocess(("pts", 1024, 9728, 256, 1), {"HKB_GEMM_PAIRS": "0"})
+    assert out["kernel"] == "gemm_fp8_kernel<256,pts>"
+    assert out["rel_err"] <= TOL, out
+
+
+def test_config4b_batched_full_size_with_bias(hk):
+    """Config 4b: B=8, M=512, N=4096, K=4096 (the CTA-pair kernel with the batch in its tile loop), with
+    the bias of the reference's batched test (tests/test_gemm.py:349-390 there)."""
+    Bn, M, N, K = 8, 512, 4096, 4096
+    aq, bq, sa, sb = _fp8_operands(M, N, K, batch=Bn, seed=24)
+    bias = torch.randn(Bn, N, generator=torch.Generator().manual_seed(5)).bfloat16()
+    C = torch.full((1, Bn, M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.a8w8.dispatch(_dev(aq).view(1, Bn, M, K), _dev(bq).view(1, Bn, N, K), _dev(sa).view(1, Bn, 1, M),
+                                  _dev(sb).view(1, Bn, 1, N), C, _dev(bias).view(1, Bn, 1, N))
+    assert hk.last_kernel() == "gemm_fp8_kernel<256,pts,pair>"
+    torch.cuda.synchronize()
+    _status_ok()
+    _sampled_rows_check(C[0], aq, bq, sa, sb, "config 4b", nrows=64, bias=bias.float().numpy())
+
+
+def test_unaligned_scale_and_bias_pointers_are_refused(hk):
+    """The epilogues read b_scale and bias with vector loads: offset views are an error, not a fault."""
+    aq, bq, sa, sb = _fp8_operands(128, 128, 128)
+    C = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    sb_off = torch.zeros(129, device=DEV)[1:]
+    with pytest.raises(RuntimeError, match="16-byte aligned"):
+        hk.gemm.a8w8_per_token.dispatch(_dev(aq), _dev(bq), C, _dev(sa), sb_off)
+    bias_off = torch.zeros(129, dtype=torch.bfloat16, device=DEV)[1:]
+    with pytest.raises(RuntimeError, match="16-byte aligned"):
+        hk.batched_gemm.a8w8.dispatch(_dev(aq), _dev(bq), _dev(sa), _dev(sb), C, bias_off)
+
+
+# ---- bounded waits -----------------------------------------------------------------------------
+
+def test_bounded_wait_gives_up_by_itself_and_the_device_stays_usable(hk):
+    """A wait that nothing will ever satisfy: the probe's producer leaves the only K block of a 128^3
+    problem unloaded and the waits are limited to 2 ms.  The MMA role gives up, raises the CTA's abort
+    flag, every role winds down, tensor memory is freed, the kernel returns; hkb_check_status() reports
+    the timeout once; an ordinary GEMM right after is correct."""
+    import ctypes
+    lib = ctypes.CDLL(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                   "amd-kernels_b200", "kernels", "libhkb200.so"))
+    lib.hkb_last_error.restype = ctypes.c_char_p
+    assert lib.hkb_check_status(None) == 0
+    aq, bq, sa, sb = _fp8_operands(128, 128, 128)
+    d = [_dev(aq), _dev(bq), _dev(sa), _dev(sb)]
+    C = torch.zeros(128, 128, dtype=torch.bfloat16, device=DEV)
+    vp = ctypes.c_void_p
+    i64 = ctypes.c_int64
+    stream = vp(torch.cuda.current_stream().cuda_stream)
+    rc = lib.hkb_debug_gemm_fp8_wait_probe(vp(d[0].data_ptr()), vp(d[1].data_ptr()), vp(C.data_ptr()), vp(d[2].data_ptr()),
+                                           vp(d[3].data_ptr()), i64(128), i64(128), i64(128), ctypes.c_uint64(2_000_000), stream)
+    assert rc == 0, lib.hkb_last_error().decode()
+    rc = lib.hkb_check_status(stream)
+    assert rc == -6, f"expected HKB_ERR_TIMEOUT, got {rc}: {lib.hkb_last_error().decode()}"
+    assert b"bounded wait" in lib.hkb_last_error()
+    assert lib.hkb_check_status(stream) == 0            # reported once, then cleared
+    C2 = torch.full((128, 128), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(d[0], d[1], C2, d[2], d[3])
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C2, gemm.gemm_fp8_per_token(aq, bq, sa, sb), "GEMM after an abandoned wait")
+
+
 # ---- block scales ---------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("shape,gn", [((128, 128, 256), 1), ((128, 128, 128), 128), ((256, 256, 512), 128),
@@ -266,6 +410,30 @@ def test_config2_full_size_sampled_rows(hk):
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:96].sort().values.to(DEV)
     ref = gemm.gemm_fp8_blockscale(aq[rows].cpu(), wq.cpu(), sa[rows].cpu(), sw.cpu())
     _check(C[rows], ref, "config 2 full size, sampled rows")
+
+
+def test_config5_single_gpu_shard_shape_sampled_rows(hk):
+    """Config 5's per-GPU problem at 8 GPUs (16384 x 7168 x 8192: one rank's column shard), config 5's
+    distributions; the oracle checks 64 sampled rows."""
+    M, N, K = 16384, 7168, 8192
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    idx = torch.randperm(K, generator=torch.Generator().manual_seed(42))[:K // 100].to(DEV)
+    A[:, idx] = (A[:, idx].float() * 20).bfloat16()
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, K // 128, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(K // 128, N // 128, device=DEV)
+    hk.fused_rmsnorm_fp8_quant_fwd(A, None, aq, sa, 1e-6)
+    hk.weight_quant_128x128(W, wq, sw)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(aq, wq, C, sa, sw)
+    assert hk.last_kernel() == "gemm_fp8_kernel<256,blockscale>"
+    torch.cuda.synchronize()
+    _status_ok()
+    assert not torch.isnan(C.float()).any()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:64].sort().values.to(DEV)
+    ref = gemm.gemm_fp8_blockscale(aq[rows].cpu(), wq.cpu(), sa[rows].cpu(), sw.cpu())
+    _check(C[rows], ref, "config 5 shard shape, sampled rows")
 
 
 # ---- MXFP4 ----------------------------------------------------------------------------------------
@@ -333,6 +501,108 @@ def test_config3_quantize_then_mxfp4_gemm_sampled(hk):
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(2))[:128].sort().values.to(DEV)
     ref = gemm.gemm_mxfp4(ac[rows].cpu(), wc.cpu(), asc[rows].cpu(), wsc.cpu())
     _check(C[rows], ref, "config 3 (M=2048) sampled rows")
+
+
+def test_config3_full_size_sampled_rows(hk):
+    """Config 3 at full size (8192^3, the CTA-pair kernel on 256 x 192 tiles); 96 sampled rows vs the oracle."""
+    M = N = K = 8192
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    ac = torch.empty(M, K // 2, dtype=torch.uint8, device=DEV); asc = torch.empty(M, K // 32, dtype=torch.uint8, device=DEV)
+    wc = torch.empty(N, K // 2, dtype=torch.uint8, device=DEV); wsc = torch.empty(N, K // 32, dtype=torch.uint8, device=DEV)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, ac, asc, 1e-6)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, wc, wsc, 1e-6)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.gemm.afp4wfp4.dispatch(ac, wc, C, asc, wsc)
+    assert hk.last_kernel() == "gemm_mxfp4_pair_kernel<256x192>"
+    torch.cuda.synchronize()
+    _status_ok()
+    assert not torch.isnan(C.float()).any()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(2))[:96].sort().values.to(DEV)
+    ref = gemm.gemm_mxfp4(ac[rows].cpu(), wc.cpu(), asc[rows].cpu(), wsc.cpu())
+    _check(C[rows], ref, "config 3 full size, sampled rows")
+
+
+def test_batched_gemm_mxfp4_wide_and_pair_kernels(hk):
+    """A batch > 1 through the CTA-pair kernel (and, with pairs switched off in a child process, through
+    the 192-wide one-CTA kernel): B=2, 2304 x 3264 x 256."""
+    Bn, M, N, K = 2, 2304, 3264, 256
+    ac, wc, asc, wsc = _mxfp4_operands(M, N, K, batch=Bn, seed=23)
+    C = torch.full((Bn, M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.afp4wfp4.dispatch(_dev(ac), _dev(wc), C, _dev(asc), _dev(wsc))
+    assert hk.last_kernel() == "gemm_mxfp4_pair_kernel<256x192>"
+    torch.cuda.synchronize()
+    _status_ok()
+    for b in range(Bn):
+        _check(C[b], gemm.gemm_mxfp4(ac[b], wc[b], asc[b], wsc[b]), f"batched mxfp4 pairs, batch {b}")
+    out = _run_case_in_subprocess(("mxfp4", M, N, K, Bn), {"HKB_MXFP4_PAIRS": "0"})
+    assert out["kernel"] == "gemm_mxfp4_kernel<192>"
+    assert out["rel_err"] <= TOL, out
+
+
+def test_mxfp4_scales_in_tensor_core_layout(hk):
+    """Scale factors handed over in the tensor core's layout (weights converted once, activations
+    quantized straight into it) give the same bits as the row-major form, with no re-layout launch."""
+    M, N, K = 2304, 3264, 384            # CTA pairs, ragged N, odd number of 128-wide K atoms
+    g = torch.Generator().manual_seed(31)
+    A = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    W = (torch.randn(N, K, generator=g) * 0.02).bfloat16().to(DEV)
+    mod = hk.gemm.afp4wfp4
+    ac = torch.empty(M, K // 2, dtype=torch.uint8, device=DEV); asc = torch.empty(M, K // 32, dtype=torch.uint8, device=DEV)
+    wc = torch.empty(N, K // 2, dtype=torch.uint8, device=DEV); wsc = torch.empty(N, K // 32, dtype=torch.uint8, device=DEV)
+    a_tc = torch.zeros(mod.sf_tc_bytes(1, M, K), dtype=torch.uint8, device=DEV)
+    w_tc = torch.full((mod.sf_tc_bytes(1, N, K),), 0xAB, dtype=torch.uint8, device=DEV)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, wc, wsc, 1e-6)
+    mod.sf_to_tc(wsc, w_tc, K)                                              # weights: converted once
+    hk.fused_rmsnorm_mxfp4_quant_tc_fwd(A, None, ac, asc, a_tc, 1e-6)       # activations: written by the quantizer
+    # the quantizer's layout equals the converter's (which also zeroes the padding the quantizer leaves alone)
+    a_tc_ref = torch.full_like(a_tc, 0xCD)
+    mod.sf_to_tc(asc, a_tc_ref, K)
+    assert torch.equal(a_tc, a_tc_ref)
+    # row-major scales of the tc quantizer equal the plain quantizer's
+    ac2 = torch.empty_like(ac); asc2 = torch.empty_like(asc)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, ac2, asc2, 1e-6)
+    assert torch.equal(ac, ac2) and torch.equal(asc, asc2)
+    C_ref = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    mod.dispatch(ac, wc, C_ref, asc, wsc)
+    for a_is_tc, b_is_tc in [(True, True), (False, True), (True, False)]:
+        C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        mod.dispatch_tc(ac, wc, C, a_tc if a_is_tc else asc, w_tc if b_is_tc else wsc, a_is_tc, b_is_tc)
+        torch.cuda.synchronize()
+        assert torch.equal(C, C_ref), (a_is_tc, b_is_tc)
+    _status_ok()
+    _check(C_ref, gemm.gemm_mxfp4(ac.cpu().numpy(), wc.cpu().numpy(), asc.cpu().numpy(), wsc.cpu().numpy()), "mxfp4 tc layout")
+    # the RMSNorm form of the quantizer writes the same layout
+    w_norm = torch.ones(K, dtype=torch.bfloat16, device=DEV)
+    a_tc3 = torch.zeros_like(a_tc); asc3 = torch.empty_like(asc); ac3 = torch.empty_like(ac)
+    hk.fused_rmsnorm_mxfp4_quant_tc_fwd(A, w_norm, ac3, asc3, a_tc3, 1e-6)
+    a_tc3_ref = torch.empty_like(a_tc)
+    mod.sf_to_tc(asc3, a_tc3_ref, K)
+    assert torch.equal(a_tc3, a_tc3_ref)
+
+
+def test_mxfp4_gemms_on_two_streams_do_not_share_scratch(hk):
+    """Two different MXFP4 GEMMs issued alternately on two streams (their scale re-layout scratch is
+    kept per stream) must both give the result they give when run alone."""
+    shapes = [(1024, 1536, 2048), (768, 2048, 2048)]
+    cases = []
+    for i, (M, N, K) in enumerate(shapes):
+        ac, wc, asc, wsc = _mxfp4_operands(M, N, K, seed=40 + i)
+        t = [_dev(x) for x in (ac, wc, asc, wsc)]
+        C_alone = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        hk.gemm.afp4wfp4.dispatch(t[0], t[1], C_alone, t[2], t[3])
+        cases.append((t, C_alone, torch.empty(M, N, dtype=torch.bfloat16, device=DEV)))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for rep in range(20):
+        for (t, _, C), st in zip(cases, streams):
+            with torch.cuda.stream(st):
+                hk.gemm.afp4wfp4.dispatch(t[0], t[1], C, t[2], t[3])
+    torch.cuda.synchronize()
+    _status_ok()
+    for t, C_alone, C in cases:
+        assert torch.equal(C, C_alone)
 
 
 # ---- fused multiply-add epilogue (C = c_a * gemm + c_b) ---------------------------------------------

@@ -62,15 +62,47 @@ def test_static_scratch_entry_point_matches_the_allocating_one_on_two_calls_in_a
         assert ogemm.rel_err(C_new.float().cpu().numpy(), oracle) <= TOL
 
 
+def test_static_scratch_entry_point_allocates_no_device_memory():
+    """The property the entry point exists for: after one warm call (which resolves the built-in
+    array's address and loads the kernels), further calls of different shapes leave the device's free
+    memory exactly where it was.  No allocating entry point runs in between."""
+    lib = _lib()
+    torch.cuda.set_device(0)
+    cases = [_case(M, N, K, seed)[0] + [M, N, K] for (M, N, K, seed) in [(256, 384, 512, 21), (200, 136, 384, 22), (1024, 640, 1024, 23)]]
+    outs = [torch.empty(c[4], c[5], dtype=torch.bfloat16, device="cuda") for c in cases]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def run(c, C):
+        p = [ctypes.c_void_p(x.data_ptr()) for x in c[:4]]
+        rc = lib.hkb_gemm_mxfp4_static(p[0], p[1], ctypes.c_void_p(C.data_ptr()), p[2], p[3], i64(1), i64(c[4]), i64(c[5]), i64(c[6]), stream)
+        assert rc == 0, lib.hkb_last_error().decode()
+
+    run(cases[0], outs[0])                       # warm call
+    torch.cuda.synchronize()
+    assert lib.hkb_check_status(stream) == 0     # reading the status words allocates nothing either
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        for c, C in zip(cases, outs):
+            run(c, C)
+    torch.cuda.synchronize()
+    assert lib.hkb_check_status(stream) == 0
+    assert torch.cuda.mem_get_info()[0] == free_before
+    for C in outs:
+        assert not torch.isnan(C.float()).any()
+
+
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
     lib = _lib()
     t, _ = _case(128, 128, 128, 13)
     p = [ctypes.c_void_p(x.data_ptr()) for x in t]
     C = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
-    # pointers are valid but the declared problem needs 16 MiB of scale scratch: refused up front
+    # pointers are valid but the declared problem needs 16 MiB of scale scratch: refused up front.
+    # (The buffers are far smaller than the declared problem, so this is only safe because the size
+    # check comes before the address look-up and before any launch.)
     rc = lib.hkb_gemm_mxfp4_static(p[0], p[1], ctypes.c_void_p(C.data_ptr()), p[2], p[3],
                                    i64(1), i64(32768), i64(32768), i64(8192), None)
     assert rc == -2
     assert b"8 MiB" in lib.hkb_last_error()
     torch.cuda.synchronize()
     assert torch.count_nonzero(C).item() == 0
+    assert lib.hkb_check_status(None) == 0
