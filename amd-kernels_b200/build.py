@@ -22,7 +22,7 @@ OUT = os.path.join(HERE, "kernels")
 OBJ = os.path.join(HERE, "build")
 EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
 
-CU_SOURCES = ["runtime.cu", "quant_fp8.cu", "quant_mxfp4.cu", "quant_moe.cu", "gemm_fp8.cu", "gemm_fp8_skinny.cu", "gemm_mxfp4.cu"]
+CU_SOURCES = ["runtime.cu", "quant_fp8.cu", "quant_mxfp4.cu", "quant_moe.cu", "gemm_fp8.cu", "gemm_fp8_skinny.cu", "gemm_mxfp4.cu", "peak_mma.cu"]
 
 # module name -> selector macro of csrc/shim.cpp
 SHIMS = {

@@ -96,6 +96,9 @@ struct GemmParams {
     int gn;                    // blockscale: 1 or 128
     const __nv_bfloat16* c_a;  // blockscale only: fused epilogue C = c_a * gemm + c_b, both [M, N]; null = plain
     const __nv_bfloat16* c_b;
+    int64_t ldc;               // row pitch of C in elements (N unless the result goes into a slab of a wider matrix)
+    __nv_bfloat16* peer[7];    // blockscale, gn = 128 only: further copies of the result (same pitch), e.g. the
+    int n_peer;                //   same slab of the other GPUs' matrices, written with plain stores from the epilogue
     uint32_t* status;
     uint64_t wait_ns;          // limit of every mbarrier wait (kWaitLimitNs in production)
     int skip_kblock;           // >= 0: the producer leaves this K block of its first tile unloaded (wait-limit probe only)
@@ -192,7 +195,9 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
     return __ffma2_rn(make_float2(__uint_as_float(a0), __uint_as_float(a1)), s, c);
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM>
+// kScatter (block-scale, 128-column weight-scale groups): the result also goes to p.n_peer further
+// destinations -- the other GPUs' copies of the assembled output.
+template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM, bool kScatter = false>
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
@@ -393,7 +398,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int row = mb * TILE_M + (int)rank * BM + row_in_tile;
             const bool row_ok = row < p.M;
             const int col_base = nb * BN + grp * COLS_PER_GROUP;
-            __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
+            __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.ldc;
 
             if constexpr (!kBlockScale) {
                 const float sa = row_ok ? __ldg(p.sa + (int64_t)b * p.M + row) : 0.0f;
@@ -499,6 +504,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         for (int i = 0; i < 8; ++i) { v[2 * i] = acc2[c / 2 + i].x; v[2 * i + 1] = acc2[c / 2 + i].y; }
                         if (p.c_a) mul_add_cols<16>(p.c_a, p.c_b, (int64_t)row * p.N + col_base + c, v);
                         store_bf16x16(crow + col_base + c, v);
+                        if constexpr (kScatter) {
+                            for (int d = 0; d < p.n_peer; ++d)      // other GPUs' copies: posted stores over NVLink
+                                store_bf16x16(p.peer[d] + (int64_t)row * p.ldc + col_base + c, v);
+                        }
                     }
                 }
             } else {
@@ -602,11 +611,11 @@ inline bool skinny_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM>
+template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM, bool kScatter = false>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
     using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0>;
     static_assert(L::kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
-    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS>;
+    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS, kScatter>;
     // the attribute is per device; set it on every call (cheap) so multi-device processes work
     const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     HKB_REQUIRE(attr_err == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(attr_err));
@@ -615,7 +624,8 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, gemm_threads<BN, kBlockScale>(), L::kDynamic, st>>>(tmA, tmB, p);
-    note_kernel(kBlockScale ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale>" : kGn128 ? "gemm_fp8_kernel<128,blockscale>" : "gemm_fp8_kernel<128,blockscale,gn1>")
+    note_kernel(kScatter ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,scatter>" : "gemm_fp8_kernel<128,blockscale,scatter>") :
+                kBlockScale ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale>" : kGn128 ? "gemm_fp8_kernel<128,blockscale>" : "gemm_fp8_kernel<128,blockscale,gn1>")
                             : (BN == 256 ? "gemm_fp8_kernel<256,pts>" : BN == 128 ? "gemm_fp8_kernel<128,pts>" : "gemm_fp8_kernel<64,pts>"));
     return check_launch("gemm_fp8_kernel");
 }
@@ -634,7 +644,8 @@ int common_checks(const char* who, const void* A, const void* B, const void* C, 
 }  // namespace
 
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
-                             const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream);
+                             const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream,
+                             int64_t ldc = 0, void* const* peers = nullptr, int n_peer = 0);
 
 // wait_ns / skip_kblock: production passes kWaitLimitNs / -1; the wait-limit probe a short limit
 // and a K block that the producer leaves unloaded.
@@ -649,6 +660,7 @@ int gemm_fp8_pts_impl(const void* A, const void* B, void* C, const float* sa, co
     GemmParams p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.sa = sa; p.sb = sb; p.bias = (const __nv_bfloat16*)bias; p.C = (__nv_bfloat16*)C; p.gn = 0;
+    p.ldc = N; p.n_peer = 0;
     p.wait_ns = wait_ns; p.skip_kblock = skip_kblock;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
@@ -713,6 +725,13 @@ int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* 
     return hkb::gemm_fp8_blockscale_impl(A, B, C, sa, sb, gn, nullptr, nullptr, M, N, K, stream);
 }
 
+int hkb_gemm_fp8_blockscale_scatter(const void* A, const void* B, void* const* C_dst, int n_dst, int64_t ldc,
+                                    const float* sa, const float* sb, int64_t M, int64_t N, int64_t K, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(C_dst && n_dst >= 1 && n_dst <= 8, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale_scatter: 1 to 8 destinations");
+    return gemm_fp8_blockscale_impl(A, B, C_dst[0], sa, sb, 128, nullptr, nullptr, M, N, K, stream, ldc, C_dst + 1, n_dst - 1);
+}
+
 int hkb_gemm_fp8_blockscale_mul_add(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                                     const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream) {
     using namespace hkb;
@@ -726,9 +745,17 @@ int hkb_gemm_fp8_blockscale_mul_add(const void* A, const void* B, void* C, const
 namespace hkb {
 
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
-                             const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream) {
+                             const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream,
+                             int64_t ldc, void* const* peers, int n_peer) {
     int rc = common_checks("gemm_fp8_blockscale", A, B, C, 1, M, N, K);
     if (rc != HKB_OK) return rc;
+    if (ldc == 0) ldc = N;
+    HKB_REQUIRE(ldc >= N && ldc % 16 == 0, HKB_ERR_BAD_SHAPE, "gemm_fp8_blockscale: row pitch %lld must be >= N and a multiple of 16", (long long)ldc);
+    HKB_REQUIRE(n_peer >= 0 && n_peer <= 7 && (n_peer == 0 || peers), HKB_ERR_BAD_ARG, "gemm_fp8_blockscale: at most 8 destinations");
+    HKB_REQUIRE((n_peer == 0 && ldc == N) || gn == 128, HKB_ERR_UNSUPPORTED,
+                "gemm_fp8_blockscale: a pitched or replicated result needs 128-column weight-scale groups");
+    for (int d = 0; d < n_peer; ++d)
+        HKB_REQUIRE(peers[d] && aligned32(peers[d]), HKB_ERR_BAD_ALIGN, "gemm_fp8_blockscale: destination %d must be non-null and 32-byte aligned", d + 1);
     HKB_REQUIRE(gn != 128 || aligned32(C), HKB_ERR_BAD_ALIGN, "gemm_fp8_blockscale: C must be 32-byte aligned");
     HKB_REQUIRE(sa && sb, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale: null scale pointer");
     HKB_REQUIRE(gn == 1 || gn == 128, HKB_ERR_UNSUPPORTED, "gemm_fp8_blockscale: weight scale group along N must be 1 or 128, got %lld", (long long)gn);
@@ -737,6 +764,8 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
     p.sa = sa; p.sb = sb; p.bias = nullptr; p.C = (__nv_bfloat16*)C; p.gn = (int)gn;
     p.c_a = (const __nv_bfloat16*)c_a; p.c_b = (const __nv_bfloat16*)c_b;
+    p.ldc = ldc; p.n_peer = n_peer;
+    for (int d = 0; d < n_peer; ++d) p.peer[d] = (__nv_bfloat16*)peers[d];
     p.wait_ns = kWaitLimitNs; p.skip_kblock = -1;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
@@ -762,6 +791,10 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
+    if (gn == 128 && n_peer > 0) {
+        if (bn == 256) return launch_gemm<256, 3, true, true, BM, true>(tmA, tmB, p, st);
+        return launch_gemm<128, 5, true, true, BM, true>(tmA, tmB, p, st);
+    }
     if (gn == 128) {
         if (bn == 256) return launch_gemm<256, 3, true, true>(tmA, tmB, p, st);
         return launch_gemm<128, 5, true, true>(tmA, tmB, p, st);

@@ -309,6 +309,30 @@ void blockscale(py::object A_, py::object B_, py::object C_, py::object sa_, py:
 [[maybe_unused]] void dispatch_blockscale(py::object A, py::object B, py::object C, py::object sa, py::object sb) {
     blockscale(A, B, C, sa, sb, py::none(), py::none());
 }
+// Not in the reference (it has no multi-GPU code): the block-scale GEMM writing its [M, N] result into
+// the same column slab of several row-major matrices of pitch ldc -- this GPU's and, through
+// peer-mapped memory, the other GPUs' copies of the assembled output.  dst_ptrs are raw device
+// addresses (first element of the slab in each destination), the local one first.
+[[maybe_unused]] void dispatch_blockscale_scatter(py::object A_, py::object B_, py::sequence dst_ptrs, int64_t ldc,
+                                                  py::object sa_, py::object sb_) {
+    TView A = view(A_, "A"), B = view(B_, "B"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale");
+    want_dtype(A, "A", {"float8_e4m3fn", "uint8"});
+    want_dtype(B, "B", {"float8_e4m3fn", "uint8"});
+    want_dtype(sa, "a_scale", {"float32"});
+    want_dtype(sb, "b_scale", {"float32"});
+    if (A.rank() != 2 || B.rank() != 2 || A.dim(1) != B.dim(1)) fail("A [M, K] and B [N, K] must be 2-D with the same K");
+    const int64_t M = A.dim(0), K = A.dim(1), N = B.dim(0);
+    if (K % 128 || N % 128) fail("K and N must be multiples of 128");
+    if (sa.numel != M * (K / 128)) fail("a_scale must be [M, K/128]");
+    if (sb.numel != (K / 128) * (N / 128)) fail("b_scale must be [K/128, N/128]");
+    std::vector<void*> dst;
+    for (auto h : dst_ptrs) dst.push_back(reinterpret_cast<void*>(h.cast<uint64_t>()));
+    if (dst.empty() || dst.size() > 8) fail("1 to 8 destinations");
+    same_device({&A, &B, &sa, &sb});
+    Launch L(A.device);
+    check(hkb_gemm_fp8_blockscale_scatter(A.ptr, B.ptr, dst.data(), (int)dst.size(), ldc, (const float*)sa.ptr,
+                                          (const float*)sb.ptr, M, N, K, L.stream));
+}
 // fused_gemm_a8w8_blockscale_mul_add_tk.dispatch(a, b, c, a_scale, b_scale, c_a, c_b):
 // kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/kernel.cpp:184-193.  C = c_a * gemm + c_b.
 [[maybe_unused]] void dispatch_blockscale_mul_add(py::object A, py::object B, py::object C, py::object sa, py::object sb,
@@ -460,6 +484,7 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_GEMM_A8W8_BLOCKSCALE)
     m.doc() = "FP8 GEMM with 1x128 activation and 128x128 (or 128x1) weight block scales, sm_100a tcgen05";
     m.def("dispatch", &dispatch_blockscale, "A"_a, "B"_a, "C"_a, "a_scale"_a, "b_scale"_a);
+    m.def("dispatch_scatter", &dispatch_blockscale_scatter, "A"_a, "B"_a, "dst_ptrs"_a, "ldc"_a, "a_scale"_a, "b_scale"_a);
 #elif defined(HKB_SHIM_GEMM_AFP4WFP4)
     m.doc() = "MXFP4 x MXFP4 GEMM (e2m1 codes, e8m0 scales per 32), sm_100a tcgen05 block-scaled MMA";
     m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());

@@ -45,8 +45,14 @@ def _default_gemm(A, B, C, a_scale, b_scale):
 
 def gemm_a8w8_blockscale(A, Wq_r, C_r, a_scale, b_scale_r, gather=False, group=None, out=None,
                          gemm_fn=None):
-    """Local shard GEMM ``C_r = blockscale(A, Wq_r)``; with ``gather=True`` also all-gathers the
-    shards and returns the assembled ``[M, N]`` tensor (``out`` if given), else returns ``C_r``.
+    """Local shard GEMM ``C_r = blockscale(A, Wq_r)``.
+
+    ``gather=False`` (default): no collective, returns ``C_r``.
+    ``gather="blocked"``: one all-gather of the bf16 shards; returns the ``[g, M, N/g]`` tensor the
+    collective produces (block r = columns of rank r), with no further copy.
+    ``gather=True``: the assembled ``[M, N]`` (``out`` if given): the blocked form re-tiled by one
+    full-size copy.  On GPUs prefer :func:`gemm_a8w8_blockscale_gathered`, which writes the assembled
+    matrix from the GEMM's epilogue and needs neither the collective nor the copy.
 
     All ranks must hold equally sized shards when gathering (N/128 divisible by the world size).
     ``gemm_fn`` replaces the CUDA GEMM in host-logic tests.
@@ -58,9 +64,56 @@ def gemm_a8w8_blockscale(A, Wq_r, C_r, a_scale, b_scale_r, gather=False, group=N
     M, n_local = C_r.shape
     blocked = torch.empty((world, M, n_local), dtype=C_r.dtype, device=C_r.device)
     dist.all_gather_into_tensor(blocked.view(world * M, n_local), C_r.contiguous(), group=group)
+    if gather == "blocked":
+        return blocked
     # [g, M, N/g] (what the collective produces) -> [M, N]
     full = blocked.permute(1, 0, 2).reshape(M, world * n_local)
     if out is not None:
         out.copy_(full)
         return out
     return full.contiguous()
+
+
+class PeerMatrix:
+    """A bf16 ``[M, N]`` matrix per rank whose storage every rank of the group can write: the target
+    of the GEMM with the all-gather fused into its epilogue.
+
+    Allocated from torch's symmetric memory (one CUDA virtual-memory allocation per rank, mapped into
+    every peer of the node over NVLink; multicast binding is not requested -- only plain peer stores
+    are used).  ``ptrs(col0)`` lists, own rank first, the device addresses of element ``[0, col0]`` in
+    every rank's copy; ``barrier()`` orders all ranks' readers behind all ranks' writers on the
+    current stream.
+    """
+
+    def __init__(self, M, N, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.M, self.N = M, N
+        self.local = symm_mem.empty((M, N), dtype=torch.bfloat16, device=device)
+        self._hdl = symm_mem.rendezvous(self.local, self.group)
+        self.rank, self.world = self._hdl.rank, self._hdl.world_size
+        self._ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def ptrs(self, col0):
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        return [self._ptrs[r] + col0 * 2 for r in order]
+
+    def barrier(self):
+        # A one-element all-reduce: it starts on a rank after that rank's GEMM (stream order) and ends
+        # only once every rank has joined, i.e. once every rank's stores have been issued and its
+        # kernel has completed.
+        dist.all_reduce(self._flag, group=self.group)
+
+
+def gemm_a8w8_blockscale_gathered(A, Wq_r, a_scale, b_scale_r, peer_out, n0):
+    """Column-sharded block-scale GEMM whose epilogue writes this rank's ``[M, N/g]`` result into columns
+    ``[n0, n0 + N/g)`` of EVERY rank's assembled matrix (``peer_out``, a :class:`PeerMatrix`): the
+    all-gather rides on the GEMM's own stores over NVLink and overlaps its main loop.  Returns
+    ``peer_out.local`` (complete after the barrier this call ends with)."""
+    from . import gemm
+    gemm.a8w8_blockscale.dispatch_scatter(A, Wq_r, peer_out.ptrs(n0), peer_out.N, a_scale, b_scale_r)
+    peer_out.barrier()
+    return peer_out.local

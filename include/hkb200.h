@@ -55,6 +55,13 @@ int hkb_debug_gemm_fp8_wait_probe(const void* A, const void* B, void* C, const f
                                   const float* sb, int64_t M, int64_t N, int64_t K,
                                   uint64_t wait_limit_ns, void* stream);
 
+/* Tensor-core ceiling probe: every SM issues `batches` x 4 back-to-back tcgen05.mma instructions
+ * (kind 0: FP8 e4m3, 128 x 256 x 32 each; kind 1: MXFP4 block-scaled, 128 x 256 x 64 each) on
+ * operand tiles resident in shared memory; no loads or stores in the loop.  The caller times the
+ * launch (CUDA events on `stream`); *flop_per_launch receives the flops it performs.  Used by the
+ * benchmark as the measured FP8 / FP4 denominator.  No counterpart in the reference project. */
+int hkb_debug_peak_mma(int kind, int64_t batches, double* flop_per_launch, void* stream);
+
 /* ---- quantizers ---------------------------------------------------------------------- */
 
 /* Per-row dynamic FP8: scales[m] = max(amax_m / 448, 1e-10), q = e4m3fn(clamp(x / scale)).
@@ -114,6 +121,19 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
 int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* sa,
                             const float* sb, int64_t gn, int64_t M, int64_t N, int64_t K,
                             void* stream);
+
+/* The block-scale GEMM (gn = 128) whose [M, N] result is written into n_dst (1..8) destinations of
+ * row pitch ldc elements (ldc >= N, ldc % 16 == 0): C_dst[i] points at the first element of the
+ * result's column slab inside destination i (32-byte aligned).  This is the column-sharded GEMM
+ * with its all-gather fused in: rank r of g passes, for every rank j, the address of columns
+ * [r*N, (r+1)*N) of rank j's assembled [M, g*N] matrix (peer-mapped device memory, its own first);
+ * the epilogue writes each finished tile to all of them with plain stores, so the transfer over
+ * NVLink overlaps the main loop of the following tiles and no collective runs afterwards.  The
+ * caller orders the readers behind every rank's launch (a barrier).  C_dst is a HOST array.
+ * No counterpart in the reference project (it has no multi-GPU code). */
+int hkb_gemm_fp8_blockscale_scatter(const void* A, const void* B, void* const* C_dst, int n_dst,
+                                    int64_t ldc, const float* sa, const float* sb, int64_t M,
+                                    int64_t N, int64_t K, void* stream);
 
 /* The same GEMM with the multiply-add epilogue fused in: C = bf16( c_a * gemm + c_b ), c_a and
  * c_b bf16 [M, N] (16-byte aligned), evaluated in fp32 before the one rounding to bf16.  Replaces

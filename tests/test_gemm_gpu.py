@@ -412,6 +412,31 @@ def test_config2_full_size_sampled_rows(hk):
     _check(C[rows], ref, "config 2 full size, sampled rows")
 
 
+@pytest.mark.parametrize("shape", [(384, 512, 512), (2304, 4608, 256)])      # 128-wide and 256-wide tile kernels
+def test_blockscale_result_scattered_into_column_slabs_of_wider_matrices(hk, shape):
+    """The multi-GPU form of the GEMM on one device: the [M, N] result goes into columns [col0, col0+N)
+    of three wider row-major matrices (stand-ins for three GPUs' assembled outputs); every copy must
+    equal the plain GEMM bit for bit and nothing outside the slab may be touched."""
+    M, N, K = shape
+    aq, bq, _, _ = _fp8_operands(M, N, K, seed=51)
+    g = torch.Generator().manual_seed(7)
+    sa = torch.rand(M, K // 128, generator=g) * 0.1 + 0.01
+    sb = torch.rand(K // 128, N // 128, generator=g) * 0.1 + 0.01
+    d = [_dev(aq), _dev(bq), _dev(sa), _dev(sb)]
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(d[0], d[1], plain, d[2], d[3])
+    ldc, col0 = 3 * N + 256, N + 128
+    outs = [torch.full((M, ldc), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    hk.gemm.a8w8_blockscale.dispatch_scatter(d[0], d[1], [o.data_ptr() + col0 * 2 for o in outs], ldc, d[2], d[3])
+    assert "scatter" in hk.last_kernel()
+    torch.cuda.synchronize()
+    _status_ok()
+    for o in outs:
+        assert torch.equal(o[:, col0:col0 + N], plain)
+        assert bool((o[:, :col0] == 7.0).all()) and bool((o[:, col0 + N:] == 7.0).all())
+    _check(plain, gemm.gemm_fp8_blockscale(aq, bq, sa, sb), f"blockscale scatter {shape}")
+
+
 def test_config5_single_gpu_shard_shape_sampled_rows(hk):
     """Config 5's per-GPU problem at 8 GPUs (16384 x 7168 x 8192: one rank's column shard), config 5's
     distributions; the oracle checks 64 sampled rows."""
