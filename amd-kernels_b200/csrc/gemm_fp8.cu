@@ -114,8 +114,8 @@ struct GemmParams {
 // behind the barriers holds, per epilogue thread and for two chunks of kScaleChunk K blocks, the
 // activation scales of the thread's row (thread-private float4 slots) and, per epilogue warp, the
 // chunk's weight scales.
-constexpr int kScaleChunk = 32;       // K blocks per chunk of staged scales
-template <int BN, int STAGES, bool kPair = false, int AROWS = BM, int SCALE_THREADS = 0>
+constexpr int kScaleChunkDefault = 32;   // K blocks per chunk of staged scales (at most 32: one lane per K block)
+template <int BN, int STAGES, bool kPair = false, int AROWS = BM, int SCALE_THREADS = 0, int kScaleChunk = kScaleChunkDefault>
 struct SmemLayout {
     static constexpr int kABytes = AROWS * BK;
     static constexpr int kTailPad = (BM - AROWS) * BK;
@@ -125,12 +125,13 @@ struct SmemLayout {
     static constexpr int kBarOffset = STAGES * kStageBytes;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
     static constexpr int kNumBars = 2 * STAGES + 4;
-    static constexpr int kScaleOffset = kBarOffset + ((kNumBars * 8 + 16 + 15) / 16) * 16;
+    // behind the barriers: tmem base, abort flag, two release counters (32 bytes in all)
+    static constexpr int kScaleOffset = kBarOffset + ((kNumBars * 8 + 32 + 15) / 16) * 16;
     static constexpr int kSaBytes = 2 * (kScaleChunk / 4) * SCALE_THREADS * 16;     // [2][chunk/4][thread] float4
     static constexpr int kSbBytes = 2 * (SCALE_THREADS / 32) * kScaleChunk * 4;     // [2][warp][chunk] float
     static constexpr int kScaleBytes = kSaBytes + kSbBytes;
     static constexpr int kTotal = SCALE_THREADS > 0 ? kScaleOffset + kScaleBytes
-                                                    : kBarOffset + (kNumBars * 8 + 16 > kTailPad ? kNumBars * 8 + 16 : kTailPad);
+                                                    : kBarOffset + (kNumBars * 8 + 32 > kTailPad ? kNumBars * 8 + 32 : kTailPad);
     static constexpr int kDynamic = kTotal + 1024;   // slack for the manual 1024-byte alignment
     static_assert(kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
@@ -197,11 +198,17 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
 
 // kScatter (block-scale, 128-column weight-scale groups): the result also goes to p.n_peer further
 // destinations -- the other GPUs' copies of the assembled output.
-template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM, bool kScatter = false>
+// VAR (block-scale, 128-column groups, one CTA): bit 0 = the epilogue hands a TMEM buffer back through a
+// shared-memory counter that the MMA thread polls, instead of an mbarrier; bit 1 = the epilogue keeps
+// two TMEM loads in flight.  kScaleChunk = K blocks per chunk of staged scales.
+template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM, bool kScatter = false,
+          int VAR = 0, int kScaleChunk = kScaleChunkDefault>
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
-    using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0>;
+    using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0, kScaleChunk>;
+    constexpr bool kCntRelease = (VAR & 1) != 0 && kBlockScale && kGn128 && !kPair;
+    constexpr bool kTwoLoads = (VAR & 2) != 0;
     static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
     constexpr int EPI_WARPS = 4 * EPI_GROUPS;
     constexpr int COLS_PER_GROUP = BN / EPI_GROUPS;
@@ -220,6 +227,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* const rel_cnt = const_cast<uint32_t*>(tmem_slot) + 2;     // [2]: epilogue warps that have released buffer a, ever
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -243,6 +251,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(tempty_bar(a), kPair ? 2 * EPI_WARPS : EPI_WARPS);   // the leader hears both CTAs' epilogues
         }
         *abort_flag = 0;
+        rel_cnt[0] = 0;
+        rel_cnt[1] = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -299,6 +309,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t ph = 0;
             int acc = 0;
             uint32_t acc_ph = 0;
+            uint32_t uses = 0;          // kCntRelease: times buffer `acc` has been filled so far (same for both when acc == 0)
             bool ok = true;
             for (int t = tile0; t < total_tiles && ok; t += tile_step) {
                 if (!kBlockScale) {
@@ -306,7 +317,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     tc_fence_after();
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (kBlockScale) {
+                    if constexpr (kCntRelease) {
+                        // all EPI_WARPS warps have read the buffer's previous contents `uses` times
+                        if (!counter_wait(smem_u32(rel_cnt + acc), uses * EPI_WARPS, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
+                        tc_fence_after();
+                    } else if (kBlockScale) {
                         if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
                         tc_fence_after();
                     }
@@ -328,7 +343,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (kBlockScale) {
                         // partial product ready for promotion
                         if constexpr (kPair) tc_commit_pair(tfull_bar(acc), 3); else tc_commit(tfull_bar(acc));
-                        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                        if (++acc == 2) { acc = 0; acc_ph ^= 1; ++uses; }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -383,7 +398,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int nsb = p.N / 128;
             const int cg = min((tnb * BN + grp * COLS_PER_GROUP) / 128, nsb - 1);
             const int kb = kb0 + lane;
-            if (kb < kblocks)
+            if (lane < kScaleChunk && kb < kblocks)
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
                              ::"r"(smem_u32(sb_slots + (size_t)buf * EPI_WARPS * kScaleChunk + lane)), "l"(p.sb + (int64_t)kb * nsb + cg) : "memory");
         };
@@ -471,6 +486,38 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     tc_fence_after();
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
                     uint32_t ra[32], rb[32];
+                    // the partial product lives in registers after the fourth load: the TMEM buffer goes back
+                    // to the MMA thread before the last FMAs
+                    auto release = [&]() {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (kCntRelease) counter_add_release(smem_u32(rel_cnt + acc));
+                            else if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0);
+                            else mbar_arrive(tempty_bar(acc));
+                        }
+                    };
+                    if constexpr (kTwoLoads) {
+                        // two loads in flight at a time: the wait covers both, so the path to the release is
+                        // two load latencies plus two FMA groups instead of four load latencies
+                        tmem_ld32(t_addr, ra);
+                        tmem_ld32(t_addr + 32, rb);
+                        tmem_ld_wait32(ra);
+                        tmem_ld_wait32(rb);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc2[j] = ffma2(ra[2 * j], ra[2 * j + 1], s2, acc2[j]);
+                        tmem_ld32(t_addr + 64, ra);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc2[16 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[16 + j]);
+                        tmem_ld32(t_addr + 96, rb);
+                        tmem_ld_wait32(ra);
+                        tmem_ld_wait32(rb);
+                        release();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc2[32 + j] = ffma2(ra[2 * j], ra[2 * j + 1], s2, acc2[32 + j]);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc2[48 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[48 + j]);
+                    } else {
                     tmem_ld32(t_addr, ra);
                     tmem_ld_wait32(ra);
                     tmem_ld32(t_addr + 32, rb);               // in flight during the FMAs on ra
@@ -485,12 +532,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc2[32 + j] = ffma2(ra[2 * j], ra[2 * j + 1], s2, acc2[32 + j]);
                     tmem_ld_wait32(rb);
-                    // the partial product now lives in registers: hand the TMEM buffer back before the last FMAs
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) { if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0); else mbar_arrive(tempty_bar(acc)); }
+                    release();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc2[48 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[48 + j]);
+                    }
                     if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                 }
                     sbuf ^= 1;
@@ -611,11 +656,12 @@ inline bool skinny_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM, bool kScatter = false>
+template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM, bool kScatter = false, int VAR = 0,
+          int SCHUNK = kScaleChunkDefault>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
-    using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0>;
+    using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0, SCHUNK>;
     static_assert(L::kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
-    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS, kScatter>;
+    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS, kScatter, VAR, SCHUNK>;
     // the attribute is per device; set it on every call (cheap) so multi-device processes work
     const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     HKB_REQUIRE(attr_err == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(attr_err));
@@ -796,7 +842,21 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
         return launch_gemm<128, 5, true, true, BM, true>(tmA, tmB, p, st);
     }
     if (gn == 128) {
-        if (bn == 256) return launch_gemm<256, 3, true, true>(tmA, tmB, p, st);
+        // HKB_BS_VARIANT (experiments): bit 0 counter release, bit 1 two TMEM loads in flight, bit 2 four
+        // stages with 8-K-block scale chunks
+        static const int var = [] { const char* v = getenv("HKB_BS_VARIANT"); return v ? atoi(v) : 0; }();
+        if (bn == 256) {
+            switch (var) {
+                case 1: return launch_gemm<256, 3, true, true, BM, false, 1>(tmA, tmB, p, st);
+                case 2: return launch_gemm<256, 3, true, true, BM, false, 2>(tmA, tmB, p, st);
+                case 3: return launch_gemm<256, 3, true, true, BM, false, 3>(tmA, tmB, p, st);
+                case 4: return launch_gemm<256, 4, true, true, BM, false, 0, 8>(tmA, tmB, p, st);
+                case 5: return launch_gemm<256, 4, true, true, BM, false, 1, 8>(tmA, tmB, p, st);
+                case 6: return launch_gemm<256, 4, true, true, BM, false, 2, 8>(tmA, tmB, p, st);
+                case 7: return launch_gemm<256, 4, true, true, BM, false, 3, 8>(tmA, tmB, p, st);
+                default: return launch_gemm<256, 3, true, true>(tmA, tmB, p, st);
+            }
+        }
         return launch_gemm<128, 5, true, true>(tmA, tmB, p, st);
     }
     return launch_gemm<128, 6, true, false>(tmA, tmB, p, st);

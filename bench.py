@@ -132,7 +132,7 @@ class ClockSampler:
         """Index of the next sample; samples from here on belong to the timed region."""
         return len(self.lines)
 
-    def stop(self, first=0):
+    def stop(self, first=0, last=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -142,7 +142,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines[first:]:
+        for ln in self.lines[first:last]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -735,6 +735,7 @@ def main():
     dom_fn = wl.gemm if is_gemm else wl.step
     barrier(world)
     dom_ms = dist_max(timed_loop(dom_fn, args.steps, 3, flush), world, dev) / args.steps
+    last_sample = sampler.mark() if rank == 0 else 0      # clock samples up to here belong to the device-resident loops
     if not is_gemm or name == "c4a":
         per_launch = (quant_bytes(wl.kind, wl.M, wl.K) if not is_gemm
                       else gemm_bytes(wl.kind, wl.batch, wl.M, wl.N, wl.K))
@@ -868,17 +869,23 @@ def main():
             else:
                 e2e["sharded_upload"] = {k: shard[k] for k in ("value", "ms_per_step", "h2d_bytes_per_step", "mode")}
 
-    # nvidia-smi samples every 100 ms; a short timed region would be missed, so the same step keeps
-    # running (untimed) until 1.5 s of load have been sampled.  Samples start with the timed steps.
-    t_load = time.time()
-    while not args.profile and time.time() - t_load < max(0.0, 1.5 - (ms + dom_ms * args.steps) / 1e3):
-        for _ in range(20):
-            wl.step()
-        torch.cuda.synchronize()
+    # nvidia-smi samples every 100 ms; a short timed region would be missed, so when the device-resident
+    # loops gave fewer than 8 samples the same step keeps running (untimed) for 1.5 s and those samples
+    # are used instead.  The end-to-end loops (PCIe-bound, GPU mostly idle) are not part of the window.
     clocks = None
+    window = "timed steps and kernel-only loop"
+    if rank == 0 and not args.profile and last_sample - first_sample < 8:
+        first_sample = sampler.mark()
+        t_load = time.time()
+        while time.time() - t_load < 1.5:
+            for _ in range(20 if dom_ms < 1.0 else 2):
+                wl.step()
+            torch.cuda.synchronize()
+        last_sample = sampler.mark()
+        window = "an untimed 1.5 s continuation of the same step right after the timed loops (the timed loops were shorter than the sampling interval)"
     if rank == 0:
-        clocks = sampler.stop(first_sample)
-        clocks["window"] = "timed steps, kernel-only loop, ceiling probe, end-to-end loops and an untimed continuation of the same step up to 1.5 s"
+        clocks = sampler.stop(first_sample, last_sample)
+        clocks["window"] = window
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

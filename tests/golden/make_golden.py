@@ -1,9 +1,9 @@
 """Generates tests/golden/*.npz by RUNNING the reference project's own Python reference
 functions (CPU, torch) -- the closest thing it has to golden vectors for the quantized-GEMM
-path.  Needs the reference checkout (default /root/reference); the fixtures it writes are
+path.  Needs a checkout of the reference project (m8than/amd-kernels); the fixtures it writes are
 committed so the test-suite never needs the checkout.
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <path to the reference checkout>
 
 Fixtures (all seed 42, the reference tests' seed):
   gemm_per_token_{M}x{N}x{K}.npz   reference_gemm_a8w8_per_token_scale
@@ -44,7 +44,7 @@ def _bf16_bits(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of the reference project's checkout")
     ref = ap.parse_args().ref
     k = os.path.join(ref, "kernels")
 

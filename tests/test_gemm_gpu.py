@@ -228,7 +228,7 @@ def _sampled_rows_check(C, aq, bq, sa, sb, what, nrows=128, bias=None):
     ((2400, 4864, 512), "gemm_fp8_kernel<256,pts,pair>"),     # last 256-row block: 96 rows, all in the leader CTA
     ((4096, 14336, 256), "gemm_fp8_kernel<256,pts,pair>"),    # config 2's M and N
     ((2048, 4608, 256), "gemm_fp8_kernel<128,pts>"),
-    ((2048, 4616, 256), "gemm_fp8_kernel<128,pts>"),          # N % 128 != 0: ragged last tile
+    ((2048, 4360, 256), "gemm_fp8_kernel<128,pts>"),          # N % 128 != 0: ragged last tile
     ((2048, 2048, 2048), "gemm_fp8_kernel<64,pts>"),
 ])
 def test_gemm_per_token_large_variants(hk, shape, kernel):
