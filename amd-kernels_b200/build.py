@@ -22,7 +22,7 @@ OUT = os.path.join(HERE, "kernels")
 OBJ = os.path.join(HERE, "build")
 EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
 
-CU_SOURCES = ["runtime.cu", "quant_fp8.cu", "quant_mxfp4.cu", "quant_moe.cu", "gemm_fp8.cu", "gemm_fp8_skinny.cu", "gemm_mxfp4.cu", "peak_mma.cu"]
+CU_SOURCES = ["runtime.cu", "quant_fp8.cu", "quant_mxfp4.cu", "quant_moe.cu", "gemm_fp8.cu", "gemm_fp8_skinny.cu", "gemm_mxfp4.cu", "peak_mma.cu", "gemm_fp8_ptgq.cu"]
 
 # module name -> selector macro of csrc/shim.cpp
 SHIMS = {
@@ -35,8 +35,11 @@ SHIMS = {
     "gemm_afp4wfp4_tk": "HKB_SHIM_GEMM_AFP4WFP4",
     "batched_gemm_a8w8_tk": "HKB_SHIM_BATCHED_GEMM_A8W8",
     "batched_gemm_afp4wfp4_tk": "HKB_SHIM_BATCHED_GEMM_AFP4WFP4",
+    "batched_gemm_a8w8_ptgq_tk": "HKB_SHIM_BATCHED_GEMM_A8W8_PTGQ",
     "fused_gemm_a8w8_blockscale_mul_add_tk": "HKB_SHIM_FUSED_GEMM_A8W8_BLOCKSCALE_MUL_ADD",
     "fused_gemm_afp4wfp4_mul_add_tk": "HKB_SHIM_FUSED_GEMM_AFP4WFP4_MUL_ADD",
+    "fused_gemm_a8w8_blockscale_split_cat_tk": "HKB_SHIM_FUSED_GEMM_A8W8_BLOCKSCALE_SPLIT_CAT",
+    "fused_gemm_afp4wfp4_split_cat_tk": "HKB_SHIM_FUSED_GEMM_AFP4WFP4_SPLIT_CAT",
     "quant_moe_tk": "HKB_SHIM_QUANT_MOE",
 }
 

@@ -99,6 +99,8 @@ struct GemmParams {
     int64_t ldc;               // row pitch of C in elements (N unless the result goes into a slab of a wider matrix)
     __nv_bfloat16* peer[7];    // blockscale, gn = 128 only: further copies of the result (same pitch), e.g. the
     int n_peer;                //   same slab of the other GPUs' matrices, written with plain stores from the epilogue
+    __nv_bfloat16* c2;         // split-cat epilogue (kOut == 2): column n = d*(s1+s2) + s of the result goes to
+    int sc_s1, sc_s2, sc_s3;   //   C[m, d, s] (row length s1+s3) when s < s1, else to c2[m, d, s-s1] (row length s2)
     uint32_t* status;
     uint64_t wait_ns;          // limit of every mbarrier wait (kWaitLimitNs in production)
     int skip_kblock;           // >= 0: the producer leaves this K block of its first tile unloaded (wait-limit probe only)
@@ -175,6 +177,15 @@ __device__ __forceinline__ void mul_add_cols(const __nv_bfloat16* c_a, const __n
     }
 }
 
+// Split-cat epilogue: where 16 consecutive result columns starting at `col` (a multiple of 16; s1, s2 and
+// s3 are multiples of 16, so a chunk never straddles a boundary) of row `row` go.
+__device__ __forceinline__ __nv_bfloat16* split_cat_ptr(const GemmParams& p, int row, int col) {
+    const int per = p.sc_s1 + p.sc_s2;
+    const int d = col / per, s = col - d * per;
+    const int64_t rd = (int64_t)row * (p.N / per) + d;
+    return s < p.sc_s1 ? p.C + rd * (p.sc_s1 + p.sc_s3) + s : p.c2 + rd * p.sc_s2 + (s - p.sc_s1);
+}
+
 // Writes 32 consecutive columns of one output row.  `wide` = rows are 32-byte aligned (N % 16 == 0);
 // otherwise 16-byte stores (N % 8 == 0 is guaranteed).
 __device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N, const float* v, bool wide) {
@@ -196,12 +207,12 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
     return __ffma2_rn(make_float2(__uint_as_float(a0), __uint_as_float(a1)), s, c);
 }
 
-// kScatter (block-scale, 128-column weight-scale groups): the result also goes to p.n_peer further
-// destinations -- the other GPUs' copies of the assembled output.
+// kOut (block-scale): 0 = plain [M, N] result; 1 = the result also goes to p.n_peer further destinations
+// (the other GPUs' copies of the assembled output; 128-column weight-scale groups only); 2 = split-cat.
 // VAR (block-scale, 128-column groups, one CTA): bit 0 = the epilogue hands a TMEM buffer back through a
 // shared-memory counter that the MMA thread polls, instead of an mbarrier; bit 1 = the epilogue keeps
 // two TMEM loads in flight.  kScaleChunk = K blocks per chunk of staged scales.
-template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM, bool kScatter = false,
+template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM, int kOut = 0,
           int VAR = 0, int kScaleChunk = kScaleChunkDefault>
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -548,10 +559,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                         for (int i = 0; i < 8; ++i) { v[2 * i] = acc2[c / 2 + i].x; v[2 * i + 1] = acc2[c / 2 + i].y; }
                         if (p.c_a) mul_add_cols<16>(p.c_a, p.c_b, (int64_t)row * p.N + col_base + c, v);
-                        store_bf16x16(crow + col_base + c, v);
-                        if constexpr (kScatter) {
-                            for (int d = 0; d < p.n_peer; ++d)      // other GPUs' copies: posted stores over NVLink
-                                store_bf16x16(p.peer[d] + (int64_t)row * p.ldc + col_base + c, v);
+                        if constexpr (kOut == 2) {
+                            store_bf16x16(split_cat_ptr(p, row, col_base + c), v);
+                        } else {
+                            store_bf16x16(crow + col_base + c, v);
+                            if constexpr (kOut == 1) {
+                                for (int d = 0; d < p.n_peer; ++d)      // other GPUs' copies: posted stores over NVLink
+                                    store_bf16x16(p.peer[d] + (int64_t)row * p.ldc + col_base + c, v);
+                            }
                         }
                     }
                 }
@@ -591,7 +606,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int c = 0; c < COLS_PER_GROUP; c += 32) {
                         if (p.c_a) mul_add_cols<32>(p.c_a, p.c_b, (int64_t)row * p.N + col_base + c, accv + c);
-                        store_row32(crow, col_base + c, p.N, accv + c, wide);
+                        if constexpr (kOut == 2) {
+                            store_bf16x16(split_cat_ptr(p, row, col_base + c), accv + c);
+                            store_bf16x16(split_cat_ptr(p, row, col_base + c + 16), accv + c + 16);
+                        } else {
+                            store_row32(crow, col_base + c, p.N, accv + c, wide);
+                        }
                     }
                 }
             }
@@ -614,6 +634,29 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 }
 
+// dst[r, off + j] = src[r, j] for j < w: the concatenation half of the split-cat epilogues
+// (rows of `w` bf16 copied into rows of pitch `ldd`), 16 bytes per thread.
+__global__ void __launch_bounds__(256)
+concat_cols_kernel(const uint4* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t rows, int w8, int64_t ldd, int64_t off) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= rows * w8) return;
+    const int64_t r = i / w8;
+    const int j = (int)(i - r * w8);
+    *reinterpret_cast<uint4*>(dst + r * ldd + off + j * 8) = __ldg(src + i);
+}
+}  // namespace
+
+int launch_concat_cols(const void* src, void* dst, int64_t rows, int64_t w, int64_t ldd, int64_t off, cudaStream_t st) {
+    HKB_REQUIRE(aligned16(src) && aligned16(dst) && w % 8 == 0 && ldd % 8 == 0 && off % 8 == 0, HKB_ERR_BAD_ALIGN,
+                "split-cat: y and c1 must be 16-byte aligned and the split sizes multiples of 8");
+    const int64_t n = rows * (w / 8);
+    if (n == 0) return HKB_OK;
+    HKB_REQUIRE((n + 255) / 256 <= 0x7FFFFFFFLL, HKB_ERR_BAD_SHAPE, "split-cat: tensor too large");
+    concat_cols_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint4*)src, (__nv_bfloat16*)dst, rows, (int)(w / 8), ldd, off);
+    return check_launch("concat_cols_kernel");
+}
+
+namespace {
 // CTA-pair launch: clusters of 2 along x, one cluster per pair of SMs, persistent over 256 x 256 tiles.
 template <int STAGES, bool kBlockScale>
 int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
@@ -656,12 +699,12 @@ inline bool skinny_enabled() {
     return on;
 }
 
-template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM, bool kScatter = false, int VAR = 0,
+template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM, int kOut = 0, int VAR = 0,
           int SCHUNK = kScaleChunkDefault>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
     using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0, SCHUNK>;
     static_assert(L::kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
-    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS, kScatter, VAR, SCHUNK>;
+    auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS, kOut, VAR, SCHUNK>;
     // the attribute is per device; set it on every call (cheap) so multi-device processes work
     const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     HKB_REQUIRE(attr_err == cudaSuccess, HKB_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", L::kDynamic, cudaGetErrorString(attr_err));
@@ -670,7 +713,8 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, gemm_threads<BN, kBlockScale>(), L::kDynamic, st>>>(tmA, tmB, p);
-    note_kernel(kScatter ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,scatter>" : "gemm_fp8_kernel<128,blockscale,scatter>") :
+    note_kernel(kOut == 1 ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,scatter>" : "gemm_fp8_kernel<128,blockscale,scatter>") :
+                kOut == 2 ? (kGn128 ? "gemm_fp8_kernel<128,blockscale,split_cat>" : "gemm_fp8_kernel<128,blockscale,gn1,split_cat>") :
                 kBlockScale ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale>" : kGn128 ? "gemm_fp8_kernel<128,blockscale>" : "gemm_fp8_kernel<128,blockscale,gn1>")
                             : (BN == 256 ? "gemm_fp8_kernel<256,pts>" : BN == 128 ? "gemm_fp8_kernel<128,pts>" : "gemm_fp8_kernel<64,pts>"));
     return check_launch("gemm_fp8_kernel");
@@ -689,9 +733,10 @@ int common_checks(const char* who, const void* A, const void* B, const void* C, 
 
 }  // namespace
 
+struct SplitCat { void* c2; int64_t s1, s2, s3; };      // C is c1 [M, D, s1+s3], c2 [M, D, s2], N = D*(s1+s2)
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                              const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream,
-                             int64_t ldc = 0, void* const* peers = nullptr, int n_peer = 0);
+                             int64_t ldc = 0, void* const* peers = nullptr, int n_peer = 0, const SplitCat* sc = nullptr);
 
 // wait_ns / skip_kblock: production passes kWaitLimitNs / -1; the wait-limit probe a short limit
 // and a K block that the producer leaves unloaded.
@@ -778,6 +823,17 @@ int hkb_gemm_fp8_blockscale_scatter(const void* A, const void* B, void* const* C
     return gemm_fp8_blockscale_impl(A, B, C_dst[0], sa, sb, 128, nullptr, nullptr, M, N, K, stream, ldc, C_dst + 1, n_dst - 1);
 }
 
+int hkb_gemm_fp8_blockscale_split_cat(const void* A, const void* B, const float* sa, const float* sb, int64_t gn,
+                                      const void* y, void* c1, void* c2, int64_t M, int64_t N, int64_t K,
+                                      int64_t S1, int64_t S2, int64_t S3, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(c1 && c2 && (S3 == 0 || y), HKB_ERR_BAD_ARG, "gemm_fp8_blockscale_split_cat: null pointer");
+    const SplitCat sc{c2, S1, S2, S3};
+    int rc = gemm_fp8_blockscale_impl(A, B, c1, sa, sb, gn, nullptr, nullptr, M, N, K, stream, 0, nullptr, 0, &sc);
+    if (rc != HKB_OK || S3 == 0) return rc;
+    return launch_concat_cols(y, c1, M * (N / (S1 + S2)), S3, S1 + S3, S1, (cudaStream_t)stream);
+}
+
 int hkb_gemm_fp8_blockscale_mul_add(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                                     const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream) {
     using namespace hkb;
@@ -792,9 +848,16 @@ namespace hkb {
 
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                              const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream,
-                             int64_t ldc, void* const* peers, int n_peer) {
+                             int64_t ldc, void* const* peers, int n_peer, const SplitCat* sc) {
     int rc = common_checks("gemm_fp8_blockscale", A, B, C, 1, M, N, K);
     if (rc != HKB_OK) return rc;
+    if (sc) {
+        HKB_REQUIRE(sc->c2 && aligned32(sc->c2) && aligned32(C), HKB_ERR_BAD_ALIGN, "gemm_fp8_blockscale_split_cat: c1 and c2 must be 32-byte aligned");
+        HKB_REQUIRE(sc->s1 > 0 && sc->s2 > 0 && sc->s3 >= 0 && sc->s1 % 16 == 0 && sc->s2 % 16 == 0 && sc->s3 % 16 == 0 &&
+                    N % (sc->s1 + sc->s2) == 0 && sc->s1 + sc->s2 + sc->s3 < (1LL << 30),
+                    HKB_ERR_BAD_SHAPE, "gemm_fp8_blockscale_split_cat: S1, S2, S3 must be multiples of 16 and N a multiple of S1+S2");
+        HKB_REQUIRE(!c_a && n_peer == 0 && ldc == 0, HKB_ERR_UNSUPPORTED, "gemm_fp8_blockscale_split_cat: no other epilogue at the same time");
+    }
     if (ldc == 0) ldc = N;
     HKB_REQUIRE(ldc >= N && ldc % 16 == 0, HKB_ERR_BAD_SHAPE, "gemm_fp8_blockscale: row pitch %lld must be >= N and a multiple of 16", (long long)ldc);
     HKB_REQUIRE(n_peer >= 0 && n_peer <= 7 && (n_peer == 0 || peers), HKB_ERR_BAD_ARG, "gemm_fp8_blockscale: at most 8 destinations");
@@ -812,6 +875,7 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     p.c_a = (const __nv_bfloat16*)c_a; p.c_b = (const __nv_bfloat16*)c_b;
     p.ldc = ldc; p.n_peer = n_peer;
     for (int d = 0; d < n_peer; ++d) p.peer[d] = (__nv_bfloat16*)peers[d];
+    if (sc) { p.c2 = (__nv_bfloat16*)sc->c2; p.sc_s1 = (int)sc->s1; p.sc_s2 = (int)sc->s2; p.sc_s3 = (int)sc->s3; }
     p.wait_ns = kWaitLimitNs; p.skip_kblock = -1;
     rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
@@ -819,7 +883,7 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     p.a_box_rows = BM;
     const int sms = sm_count();
     int bn = 256;
-    if (gn != 128 || N % 256 != 0 || (int64_t)p.m_blks * (N / 256) < 2LL * sms) bn = 128;
+    if (gn != 128 || sc || N % 256 != 0 || (int64_t)p.m_blks * (N / 256) < 2LL * sms) bn = 128;
     p.n_blks = (int)(N / bn);
     cudaStream_t st = (cudaStream_t)stream;
     CUtensorMap tmA, tmB;
@@ -837,9 +901,13 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     }
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)bn);
     if (rc != HKB_OK) return rc;
+    if (sc) {
+        if (gn == 128) return launch_gemm<128, 5, true, true, BM, 2>(tmA, tmB, p, st);
+        return launch_gemm<128, 6, true, false, BM, 2>(tmA, tmB, p, st);
+    }
     if (gn == 128 && n_peer > 0) {
-        if (bn == 256) return launch_gemm<256, 3, true, true, BM, true>(tmA, tmB, p, st);
-        return launch_gemm<128, 5, true, true, BM, true>(tmA, tmB, p, st);
+        if (bn == 256) return launch_gemm<256, 3, true, true, BM, 1>(tmA, tmB, p, st);
+        return launch_gemm<128, 5, true, true, BM, 1>(tmA, tmB, p, st);
     }
     if (gn == 128) {
         // HKB_BS_VARIANT (experiments): bit 0 counter release, bit 1 two TMEM loads in flight, bit 2 four
@@ -847,13 +915,13 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
         static const int var = [] { const char* v = getenv("HKB_BS_VARIANT"); return v ? atoi(v) : 0; }();
         if (bn == 256) {
             switch (var) {
-                case 1: return launch_gemm<256, 3, true, true, BM, false, 1>(tmA, tmB, p, st);
-                case 2: return launch_gemm<256, 3, true, true, BM, false, 2>(tmA, tmB, p, st);
-                case 3: return launch_gemm<256, 3, true, true, BM, false, 3>(tmA, tmB, p, st);
-                case 4: return launch_gemm<256, 4, true, true, BM, false, 0, 8>(tmA, tmB, p, st);
-                case 5: return launch_gemm<256, 4, true, true, BM, false, 1, 8>(tmA, tmB, p, st);
-                case 6: return launch_gemm<256, 4, true, true, BM, false, 2, 8>(tmA, tmB, p, st);
-                case 7: return launch_gemm<256, 4, true, true, BM, false, 3, 8>(tmA, tmB, p, st);
+                case 1: return launch_gemm<256, 3, true, true, BM, 0, 1>(tmA, tmB, p, st);
+                case 2: return launch_gemm<256, 3, true, true, BM, 0, 2>(tmA, tmB, p, st);
+                case 3: return launch_gemm<256, 3, true, true, BM, 0, 3>(tmA, tmB, p, st);
+                case 4: return launch_gemm<256, 4, true, true, BM, 0, 0, 8>(tmA, tmB, p, st);
+                case 5: return launch_gemm<256, 4, true, true, BM, 0, 1, 8>(tmA, tmB, p, st);
+                case 6: return launch_gemm<256, 4, true, true, BM, 0, 2, 8>(tmA, tmB, p, st);
+                case 7: return launch_gemm<256, 4, true, true, BM, 0, 3, 8>(tmA, tmB, p, st);
                 default: return launch_gemm<256, 3, true, true>(tmA, tmB, p, st);
             }
         }

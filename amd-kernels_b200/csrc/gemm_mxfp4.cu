@@ -37,6 +37,8 @@ struct Mxfp4Params {
     __nv_bfloat16* C;
     const __nv_bfloat16* c_a;     // fused multiply-add epilogue C = c_a * (A B^T) + c_b, both [batch, M, N]; null = plain
     const __nv_bfloat16* c_b;
+    __nv_bfloat16* c2;            // split-cat epilogue (sc_s1 > 0, one-CTA kernels, batch 1): column n = d*(s1+s2) + s goes to
+    int sc_s1, sc_s2, sc_s3;      //   C[m, d, s] (row length s1+s3) when s < s1, else to c2[m, d, s-s1] (row length s2)
     uint32_t* status;
 };
 
@@ -263,7 +265,14 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             o.y = *reinterpret_cast<uint32_t*>(&q1);
                             o.z = *reinterpret_cast<uint32_t*>(&q2);
                             o.w = *reinterpret_cast<uint32_t*>(&q3);
-                            *reinterpret_cast<uint4*>(crow + col0 + j) = o;
+                            __nv_bfloat16* dst = crow + col0 + j;
+                            if (p.sc_s1) {          // split-cat: 8 columns never straddle a boundary (sizes are multiples of 16)
+                                const int per = p.sc_s1 + p.sc_s2, col = col0 + j;
+                                const int d = col / per, sidx = col - d * per;
+                                const int64_t rd = (int64_t)row * (p.N / per) + d;
+                                dst = sidx < p.sc_s1 ? p.C + rd * (p.sc_s1 + p.sc_s3) + sidx : p.c2 + rd * p.sc_s2 + (sidx - p.sc_s1);
+                            }
+                            *reinterpret_cast<uint4*>(dst) = o;
                         }
                     }
                 }
@@ -530,8 +539,11 @@ int launch_sf_relayout(const void* src, void* dst, int64_t batch, int64_t R, int
 // sfa_tc / sfb_tc: the scale pointer already is in the tensor-core layout (hkb_mxfp4_sf_to_tc or
 // hkb_quant_mxfp4_tc); otherwise it is row-major [batch, rows, K/32] and is re-laid-out into
 // per-(device, stream) scratch first.
+struct SplitCat { void* c2; int64_t s1, s2, s3; };      // C is c1 [M, D, s1+s3], c2 [M, D, s2], N = D*(s1+s2)
+
 int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, const void* sfb, bool sfa_tc, bool sfb_tc,
-                    const void* c_a, const void* c_b, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+                    const void* c_a, const void* c_b, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream,
+                    const SplitCat* sc = nullptr) {
     HKB_REQUIRE(A && B && C && sfa && sfb, HKB_ERR_BAD_ARG, "gemm_mxfp4: null pointer");
     HKB_REQUIRE(batch >= 1 && M >= 1 && N >= 1 && K >= 1, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: empty problem");
     HKB_REQUIRE(K % 128 == 0, HKB_ERR_BAD_SHAPE, "gemm_mxfp4: K=%lld must be a multiple of 128", (long long)K);
@@ -557,13 +569,21 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
     p.C = (__nv_bfloat16*)C;
     p.c_a = (const __nv_bfloat16*)c_a;
     p.c_b = (const __nv_bfloat16*)c_b;
+    if (sc) {
+        HKB_REQUIRE(batch == 1 && !c_a, HKB_ERR_UNSUPPORTED, "gemm_mxfp4_split_cat: 2-D operands, no other epilogue at the same time");
+        HKB_REQUIRE(sc->c2 && aligned16(sc->c2), HKB_ERR_BAD_ALIGN, "gemm_mxfp4_split_cat: c2 must be 16-byte aligned");
+        HKB_REQUIRE(sc->s1 > 0 && sc->s2 > 0 && sc->s3 >= 0 && sc->s1 % 16 == 0 && sc->s2 % 16 == 0 && sc->s3 % 16 == 0 &&
+                    N % (sc->s1 + sc->s2) == 0 && sc->s1 + sc->s2 + sc->s3 < (1LL << 30),
+                    HKB_ERR_BAD_SHAPE, "gemm_mxfp4_split_cat: S1, S2, S3 must be multiples of 16 and N a multiple of S1+S2");
+        p.c2 = (__nv_bfloat16*)sc->c2; p.sc_s1 = (int)sc->s1; p.sc_s2 = (int)sc->s2; p.sc_s3 = (int)sc->s3;
+    }
     int rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
 
     // CTA pairs on 256 x 192 tiles when there is at least half a wave of them (HKB_MXFP4_PAIRS=0: never)
     static const bool pairs_on = [] { const char* v = getenv("HKB_MXFP4_PAIRS"); return !(v && v[0] == '0'); }();
     const int64_t pair_tiles = ((M + 255) / 256) * ((N + 191) / 192) * batch;
-    const bool pair = pairs_on && wide && M > 128 && pair_tiles >= sms / 2 && sms >= 2;
+    const bool pair = pairs_on && wide && M > 128 && pair_tiles >= sms / 2 && sms >= 2 && !sc;     // the split-cat store lives in the one-CTA kernels
 
     const size_t sfa_bytes = (size_t)batch * p.sfa_rblks * p.katoms * 512;
     const size_t sfb_bytes = (size_t)batch * p.sfb_rblks * p.katoms * 512;
@@ -646,6 +666,17 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
 extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                               int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
     return hkb::gemm_mxfp4_impl(A, B, C, sfa, sfb, false, false, nullptr, nullptr, batch, M, N, K, stream);
+}
+
+extern "C" int hkb_gemm_mxfp4_split_cat(const void* A, const void* B, const void* sfa, const void* sfb, const void* y,
+                                        void* c1, void* c2, int64_t M, int64_t N, int64_t K, int64_t S1, int64_t S2,
+                                        int64_t S3, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(c1 && c2 && (S3 == 0 || y), HKB_ERR_BAD_ARG, "gemm_mxfp4_split_cat: null pointer");
+    const SplitCat sc{c2, S1, S2, S3};
+    int rc = gemm_mxfp4_impl(A, B, c1, sfa, sfb, false, false, nullptr, nullptr, 1, M, N, K, stream, &sc);
+    if (rc != HKB_OK || S3 == 0) return rc;
+    return launch_concat_cols(y, c1, M * (N / (S1 + S2)), S3, S1 + S3, S1, (cudaStream_t)stream);
 }
 
 extern "C" int64_t hkb_mxfp4_sf_tc_bytes(int64_t batch, int64_t rows, int64_t K) {

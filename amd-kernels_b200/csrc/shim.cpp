@@ -271,6 +271,24 @@ void fp8_pts(py::object A_, py::object B_, py::object C_, py::object sa_, py::ob
     fp8_pts(A, B, C, sa, sb, bias);
 }
 
+// batched_gemm_a8w8_ptgq dispatch(a, b, b_scale, c, bias):
+// kernels/gemm-batched/batched_gemm_a8w8_ptgq/kernel.cpp:241-249.  a bf16 [.., M, K] (quantized per row and
+// 64-wide K group inside the kernel), b e4m3fn codes [.., N, K], b_scale one float, bias bf16 [.., 1, N] or None.
+[[maybe_unused]] void dispatch_ptgq(py::object A_, py::object B_, py::object bs_, py::object C_, py::object bias_) {
+    TView A = view(A_, "a"), B = view(B_, "b"), bs = view(bs_, "b_scale"), C = view(C_, "c"), bias = view(bias_, "bias", true);
+    want_dtype(A, "a", {"bfloat16"});
+    want_dtype(B, "b", {"float8_e4m3fn", "uint8"});
+    want_dtype(bs, "b_scale", {"float32"});
+    want_dtype(C, "c", {"bfloat16"});
+    if (!bias.none) want_dtype(bias, "bias", {"bfloat16"});
+    GemmDims d = gemm_dims(A, B, C, 1, 1);
+    if (bs.numel != 1) fail("b_scale must hold one float (per-tensor weight scale)");
+    if (!bias.none && bias.numel != d.batch * d.N) fail("bias must have batch*N elements");
+    same_device({&A, &B, &bs, &C, &bias});
+    Launch L(A.device);
+    check(hkb_gemm_fp8_ptgq(A.ptr, B.ptr, (const float*)bs.ptr, C.ptr, bias.none ? nullptr : bias.ptr, d.batch, d.M, d.N, d.K, L.stream));
+}
+
 // gemm_a8w8_blockscale_tk.dispatch(A, B, C, a_scale, b_scale):
 // kernels/gemm-basic/gemm_a8w8_blockscale/kernel.cpp:174-180.
 // a_scale [M, K/128]; b_scale [K/128, N/gn], gn = N / b_scale.shape[1] in {1, 128}.
@@ -414,6 +432,58 @@ void mxfp4(py::object A_, py::object B_, py::object C_, py::object sfa_, py::obj
     mxfp4(A, B, C, sfa, sfb, ca, cb);
 }
 
+// Split-cat epilogues: dispatch(a, b, a_scale, b_scale, y, c1, c2), the field order of the reference's
+// globals structs (kernels/gemm-fused/fused_gemm_a8w8_blockscale_split_cat/kernel.cpp:34-45,
+// fused_gemm_afp4wfp4_split_cat/kernel.cpp:34-45; the reference binds neither to Python).
+// y [M, D, S3], c1 [M, D, S1+S3], c2 [M, D, S2]; D, S1, S2, S3 are read from those shapes.
+struct SplitDims { int64_t D, S1, S2, S3; };
+SplitDims split_dims(const TView& y, const TView& c1, const TView& c2, int64_t M, int64_t N) {
+    if (y.rank() != 3 || c1.rank() != 3 || c2.rank() != 3) fail("y, c1, c2 must be [M, D, S]");
+    SplitDims d{c2.dim(1), c1.dim(2) - y.dim(2), c2.dim(2), y.dim(2)};
+    if (y.dim(0) != M || c1.dim(0) != M || c2.dim(0) != M || y.dim(1) != d.D || c1.dim(1) != d.D) fail("y, c1, c2 must agree on M and D");
+    if (d.S1 <= 0 || d.D * (d.S1 + d.S2) != N) fail("N must equal D * (S1 + S2)");
+    return d;
+}
+[[maybe_unused]] void dispatch_blockscale_split_cat(py::object A_, py::object B_, py::object sa_, py::object sb_, py::object y_,
+                                                    py::object c1_, py::object c2_) {
+    TView A = view(A_, "a"), B = view(B_, "b"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale"), y = view(y_, "y"),
+          c1 = view(c1_, "c1"), c2 = view(c2_, "c2");
+    want_dtype(A, "a", {"float8_e4m3fn", "uint8"});
+    want_dtype(B, "b", {"float8_e4m3fn", "uint8"});
+    want_dtype(sa, "a_scale", {"float32"});
+    want_dtype(sb, "b_scale", {"float32"});
+    for (const TView* t : {&y, &c1, &c2}) want_dtype(*t, t->name, {"bfloat16"});
+    if (A.rank() != 2 || B.rank() != 2 || A.dim(1) != B.dim(1)) fail("a [M, K] and b [N, K] must be 2-D with the same K");
+    const int64_t M = A.dim(0), K = A.dim(1), N = B.dim(0);
+    if (K % 128) fail("K must be a multiple of 128");
+    const SplitDims d = split_dims(y, c1, c2, M, N);
+    const int64_t kb = K / 128;
+    if (sa.numel != M * kb) fail("a_scale must be [M, K/128]");
+    if (sb.numel != kb * N && sb.numel * 128 != kb * N) fail("b_scale must be [K/128, N] or [K/128, N/128]");
+    const int64_t gn = sb.numel == kb * N ? 1 : 128;
+    same_device({&A, &B, &sa, &sb, &y, &c1, &c2});
+    Launch L(A.device);
+    check(hkb_gemm_fp8_blockscale_split_cat(A.ptr, B.ptr, (const float*)sa.ptr, (const float*)sb.ptr, gn, y.ptr, c1.ptr, c2.ptr,
+                                            M, N, K, d.S1, d.S2, d.S3, L.stream));
+}
+[[maybe_unused]] void dispatch_mxfp4_split_cat(py::object A_, py::object B_, py::object sfa_, py::object sfb_, py::object y_,
+                                               py::object c1_, py::object c2_) {
+    TView A = view(A_, "a"), B = view(B_, "b"), sfa = view(sfa_, "a_scale"), sfb = view(sfb_, "b_scale"), y = view(y_, "y"),
+          c1 = view(c1_, "c1"), c2 = view(c2_, "c2");
+    want_dtype(A, "a", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(B, "b", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(sfa, "a_scale", {"uint8", "float8_e8m0fnu"});
+    want_dtype(sfb, "b_scale", {"uint8", "float8_e8m0fnu"});
+    for (const TView* t : {&y, &c1, &c2}) want_dtype(*t, t->name, {"bfloat16"});
+    if (A.rank() != 2 || B.rank() != 2 || A.dim(1) != B.dim(1)) fail("a [M, K/2] and b [N, K/2] must be 2-D with the same K");
+    const int64_t M = A.dim(0), K = A.dim(1) * 2, N = B.dim(0);
+    const SplitDims d = split_dims(y, c1, c2, M, N);
+    if (sfa.numel != M * (K / 32) || sfb.numel != N * (K / 32)) fail("a_scale / b_scale must be [rows, K/32]");
+    same_device({&A, &B, &sfa, &sfb, &y, &c1, &c2});
+    Launch L(A.device);
+    check(hkb_gemm_mxfp4_split_cat(A.ptr, B.ptr, sfa.ptr, sfb.ptr, y.ptr, c1.ptr, c2.ptr, M, N, K, d.S1, d.S2, d.S3, L.stream));
+}
+
 // quant_moe_tk: kernels/moe-misc/quant_moe/kernel.cpp:392-476 (same names, argument order and the
 // redundant integer size arguments, which are checked against the tensors).
 [[maybe_unused]] void downcast_to_static_fp8(py::object x_, py::object y_, py::object scale_, int64_t M, int64_t N) {
@@ -494,6 +564,9 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_BATCHED_GEMM_A8W8)
     m.doc() = "batched FP8 GEMM with per-token / per-channel scales and optional bias, sm_100a tcgen05";
     m.def("dispatch", &dispatch_batched_a8w8, "A"_a, "B"_a, "a_scale"_a, "b_scale"_a, "C"_a, "bias"_a = py::none());
+#elif defined(HKB_SHIM_BATCHED_GEMM_A8W8_PTGQ)
+    m.doc() = "batched FP8 GEMM with in-loop per-row, per-64-K-group activation quantization and a scalar weight scale, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_ptgq, "a"_a, "b"_a, "b_scale"_a, "c"_a, "bias"_a = py::none());
 #elif defined(HKB_SHIM_BATCHED_GEMM_AFP4WFP4)
     m.doc() = "batched MXFP4 x MXFP4 GEMM, sm_100a tcgen05 block-scaled MMA";
     m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());
@@ -503,6 +576,12 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_FUSED_GEMM_AFP4WFP4_MUL_ADD)
     m.doc() = "MXFP4 x MXFP4 GEMM with fused multiply-add epilogue C = c_a * gemm + c_b, sm_100a tcgen05";
     m.def("dispatch", &dispatch_mxfp4_mul_add, "a"_a, "b"_a, "c"_a, "a_scale"_a, "b_scale"_a, "c_a"_a, "c_b"_a);
+#elif defined(HKB_SHIM_FUSED_GEMM_A8W8_BLOCKSCALE_SPLIT_CAT)
+    m.doc() = "block-scale FP8 GEMM with the split-concatenate epilogue (c1, c2 written from the epilogue), sm_100a tcgen05";
+    m.def("dispatch", &dispatch_blockscale_split_cat, "a"_a, "b"_a, "a_scale"_a, "b_scale"_a, "y"_a, "c1"_a, "c2"_a);
+#elif defined(HKB_SHIM_FUSED_GEMM_AFP4WFP4_SPLIT_CAT)
+    m.doc() = "MXFP4 x MXFP4 GEMM with the split-concatenate epilogue, sm_100a tcgen05";
+    m.def("dispatch", &dispatch_mxfp4_split_cat, "a"_a, "b"_a, "a_scale"_a, "b_scale"_a, "y"_a, "c1"_a, "c2"_a);
 #elif defined(HKB_SHIM_QUANT_MOE)
     m.doc() = "MoE casts: static FP8 down-cast, MX (e4m3 / e2m1 + exponent byte per 32) down- and up-cast, sm_100a";
     m.def("downcast_to_static_fp8", &downcast_to_static_fp8, "x"_a, "y"_a, "scale"_a, "M"_a, "N"_a);

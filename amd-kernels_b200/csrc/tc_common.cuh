@@ -23,6 +23,9 @@ int make_tmap_linear1k(CUtensorMap* map, const void* base, uint64_t bytes);
 int launch_gemm_fp8_skinny(const void* A, const void* B, void* C, const float* sa, const float* sb, const void* bias,
                            int64_t M, int64_t N, int64_t K, uint32_t* status, cudaStream_t st);
 
+// dst[r, off + j] = src[r, j], j < w (bf16, 16-byte vectors): the concatenation of the split-cat epilogues.
+int launch_concat_cols(const void* src, void* dst, int64_t rows, int64_t w, int64_t ldd, int64_t off, cudaStream_t st);
+
 // ---- device --------------------------------------------------------------------------------
 constexpr uint32_t kErrWaitProducer = 1u;   // status bits OR-ed into the device status word
 constexpr uint32_t kErrWaitMma = 2u;

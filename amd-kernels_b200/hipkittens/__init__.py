@@ -12,6 +12,7 @@ re-implemented for NVIDIA B200 (sm_100a) behind the same module and function nam
     hk.gemm.afp4wfp4.dispatch(A, B, C, a_scales, b_scales)
     hk.batched_gemm.a8w8.dispatch(A, B, a_scale, b_scale, C, bias)
     hk.batched_gemm.afp4wfp4.dispatch(A, B, C, a_scales, b_scales)
+    hk.batched_gemm.a8w8_ptgq.dispatch(a_bf16, b, b_scale, c, bias)
     hk.modules['quant_tk'].per_token_quant_fwd(...)
 
 The loader mirrors the reference's (hipkittens/__init__.py:31-111,209-304 there): compiled
@@ -179,6 +180,7 @@ class _GemmNamespace:
 
 class _BatchedGemmNamespace:
     a8w8 = _SubModule("batched_gemm_a8w8_tk")
+    a8w8_ptgq = _SubModule("batched_gemm_a8w8_ptgq_tk")    # bf16 activations quantized per 64-K group inside the GEMM
     afp4wfp4 = _SubModule("batched_gemm_afp4wfp4_tk")
     bf16 = _SubModule("batched_gemm_bf16_tk")
     a16wfp4 = _SubModule("batched_gemm_a16wfp4_tk")
@@ -188,6 +190,9 @@ class _FusedGemmNamespace:
     # quantized GEMM + multiply-add epilogue (C = c_a * gemm + c_b)
     a8w8_blockscale_mul_add = _SubModule("fused_gemm_a8w8_blockscale_mul_add_tk")
     afp4wfp4_mul_add = _SubModule("fused_gemm_afp4wfp4_mul_add_tk")
+    # quantized GEMM + split-concatenate epilogue (c1[:, d, :S1] | y, c2[:, d, :S2])
+    a8w8_blockscale_split_cat = _SubModule("fused_gemm_a8w8_blockscale_split_cat_tk")
+    afp4wfp4_split_cat = _SubModule("fused_gemm_afp4wfp4_split_cat_tk")
     # names kept for compatibility; not built here (each pairs the quantized GEMM with a bf16 GEMM)
     a8w8_blockscale_a16w16 = _SubModule("fused_gemm_a8w8_blockscale_a16w16_tk")
     afp4wfp4_a16w16 = _SubModule("fused_gemm_afp4wfp4_a16w16_tk")

@@ -251,11 +251,17 @@ class Workload:
             self.Wq = torch.empty(self.N, K // 2, dtype=torch.uint8, device=dev)
             self.sw = torch.empty(self.N, K // 32, dtype=torch.uint8, device=dev)
             hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, self.Wq, self.sw, 1e-6)
+            # resident weights: their scales are converted to the tensor core's layout once; the activation
+            # quantizer writes that layout directly, so a step is two launches (quantizer, GEMM)
+            mod = hk.gemm.afp4wfp4
+            self.sw_tc = torch.zeros(mod.sf_tc_bytes(1, self.N, K), dtype=torch.uint8, device=dev)
+            mod.sf_to_tc(self.sw, self.sw_tc, K)
             self.Aq = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
             self.sa = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+            self.sa_tc = torch.zeros(mod.sf_tc_bytes(1, M, K), dtype=torch.uint8, device=dev)
         cshape = (M, self.N) if B == 1 else (B, M, self.N)
         self.C = torch.empty(cshape, dtype=torch.bfloat16, device=dev)
-        self.launches_per_step = 2 if self.kind != "mxfp4" else 4     # quant + gemm (+ 2 scale re-layouts)
+        self.launches_per_step = 2                                      # quantizer + GEMM
         torch.cuda.synchronize()
 
     # -- device-resident step ------------------------------------------------------------
@@ -266,7 +272,7 @@ class Workload:
         elif self.kind == "pts":
             hk.per_token_quant_fwd(A.view(-1, K), self.Aq.view(-1, K), self.sa)
         elif self.kind == "mxfp4":
-            hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
+            hk.fused_rmsnorm_mxfp4_quant_tc_fwd(A, None, self.Aq, None, self.sa_tc, 1e-6)
         elif self.kind == "quant-fp8":
             hk.per_token_quant_fwd(self.x, self.q, self.s)
         elif self.kind in ("quant-1x128", "quant-rms-1x128"):
@@ -295,7 +301,7 @@ class Workload:
             else:
                 hk.batched_gemm.a8w8.dispatch(self.Aq, self.Wq, self.sa, self.sw, C, None)
         elif self.kind == "mxfp4":
-            hk.gemm.afp4wfp4.dispatch(self.Aq, self.Wq, C, self.sa, self.sw)
+            hk.gemm.afp4wfp4.dispatch_tc(self.Aq, self.Wq, C, self.sa_tc, self.sw_tc, True, True)
 
     def step(self):
         if self.kind.startswith("quant"):

@@ -114,6 +114,19 @@ int hkb_gemm_fp8_pts(const void* A, const void* B, void* C, const float* sa, con
                      const void* bias_or_null, int64_t batch, int64_t M, int64_t N, int64_t K,
                      void* stream);
 
+/* Batched GEMM with the activation quantizer inside the main loop.  A bf16 [batch, M, K] is quantized
+ * per row and per 64-wide K group while it is staged: m = max(|A_g|, 1e-10), a_scale = m * (1/448),
+ * q = e4m3fn(clamp(A_g * (1/a_scale), +-448)); C[b] = bf16( (sum_g (q_g @ B_g^T) * a_scale_g) * b_scale
+ * + bias[b] ), fp32 throughout.  B e4m3fn codes [batch, N, K], b_scale ONE float (per-tensor weight
+ * scale, device memory), bias bf16 [batch, N] or NULL.  K % 64 == 0, N % 8 == 0; A 32-byte, B, C and
+ * bias 16-byte aligned.  Replaces dispatch(a, b, b_scale, c, bias) of
+ *   kernels/gemm-batched/batched_gemm_a8w8_ptgq/kernel.cpp:168-215,241-249
+ * re-targeted from the INT8 range (127, no rounding of the quantized values in the reference's
+ * arithmetic) to e4m3fn (448, round-to-nearest-even), the expression order kept. */
+int hkb_gemm_fp8_ptgq(const void* A, const void* B, const float* b_scale, void* C,
+                      const void* bias_or_null, int64_t batch, int64_t M, int64_t N, int64_t K,
+                      void* stream);
+
 /* C = bf16( sum_kb (A_kb @ B_kb^T) * sa[m, kb] * sb[kb, n / gn] ), e4m3fn operands,
  * sa f32 [M, K/128], sb f32 [K/128, N/gn], gn in {1, 128}.  K % 128 == 0, N % 128 == 0.
  * Replaces gemm_a8w8_blockscale_tk.dispatch(A,B,C,a_scale,b_scale):
@@ -192,6 +205,23 @@ int hkb_quant_mxfp4_tc(const void* x, const void* w_or_null, void* codes, void* 
 int hkb_gemm_mxfp4_mul_add(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                            const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K,
                            void* stream);
+
+/* The block-scale FP8 and the MXFP4 GEMM with the split-concatenate epilogue: with N = D*(S1+S2), column
+ * n = d*(S1+S2) + s of the [M, N] result goes to c1[m, d, s] when s < S1 and to c2[m, d, s-S1] otherwise;
+ * y [M, D, S3] is copied behind the first part, c1[m, d, S1:S1+S3] = y[m, d, :].  c1 bf16 [M, D, S1+S3],
+ * c2 bf16 [M, D, S2], written straight from the GEMMs' epilogues (no [M, N] intermediate).  S1, S2, S3
+ * multiples of 16 (S3 may be 0); c1, c2 32-byte, y 16-byte aligned; other arguments as for
+ * hkb_gemm_fp8_blockscale / hkb_gemm_mxfp4 (batch 1).  Replace
+ *   dispatch_fused_gemm_a8w8_bs_split_cat   kernels/gemm-fused/fused_gemm_a8w8_blockscale_split_cat/kernel.cpp:34-50,168-247
+ *   dispatch_fused_gemm_afp4wfp4_split_cat  kernels/gemm-fused/fused_gemm_afp4wfp4_split_cat/kernel.cpp:34-45
+ * (the reference gives these two no Python binding; its b_scale there is [K/128, N], gn = 1). */
+int hkb_gemm_fp8_blockscale_split_cat(const void* A, const void* B, const float* sa, const float* sb,
+                                      int64_t gn, const void* y, void* c1, void* c2, int64_t M,
+                                      int64_t N, int64_t K, int64_t S1, int64_t S2, int64_t S3,
+                                      void* stream);
+int hkb_gemm_mxfp4_split_cat(const void* A, const void* B, const void* sfa, const void* sfb,
+                             const void* y, void* c1, void* c2, int64_t M, int64_t N, int64_t K,
+                             int64_t S1, int64_t S2, int64_t S3, void* stream);
 
 /* quant_moe_tk: wire formats of the MoE activation/weight casts.  Replace
  *   quant_moe_tk.downcast_to_static_fp8(x, y, scale, M, N)

@@ -7,6 +7,7 @@ Expressions followed:
   mxfp4       kernels/gemm-basic/gemm_afp4wfp4/test_parity.py:30-31 on operands dequantized as
               kernels/moe-gemm/moe_op_mxfp4/test_parity.py:36-46
   batched     tests/test_gemm.py:366-367 (bias added in fp32 before the bf16 store)
+  ptgq        kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:40-82 (in-loop re-quantization)
   metric      tests/test_gemm.py:190-192
 """
 import numpy as np
@@ -108,11 +109,55 @@ def gemm_group32_f32(A, B, sa, sb, group=32):
     return C.numpy()
 
 
+def gemm_ptgq(A, B, b_scale, bias=None, group=64, qmax=448.0, qmin=-448.0, cast="e4m3"):
+    """GEMM with per-row, per-`group`-K dynamic quantization of A inside the K loop, restating
+    kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:56-77 line by line (all fp32):
+        m = clamp(max|A_g|, min=1e-10); a_scale = m * (1/qmax); recip = 1 / a_scale
+        A_q = clamp(A_g * recip, qmin, qmax)   [then `cast`]
+        acc += (A_q @ B_g^T) * a_scale;  after the loop acc *= b_scale;  acc += bias
+    A [.., M, K] (bf16 values), B [.., N, K] decoded weight values, bias [.., 1, N] or None.
+    The reference's own arithmetic is qmax=127, qmin=-128, cast=None (its quantized values are never
+    rounded); the B200 build's is the default: e4m3fn range and round-to-nearest-even cast."""
+    from .codecs import f32_to_e4m3fn
+    A = _f32(A)
+    B = _f32(B)
+    K = A.shape[-1]
+    acc = torch.zeros(*A.shape[:-1], B.shape[-2], dtype=torch.float32)
+    inv = np.float32(1.0 / qmax)
+    for k0 in range(0, K, group):
+        Ag = A[..., k0:k0 + group]
+        m = np.maximum(np.abs(Ag).max(axis=-1, keepdims=True), np.float32(1e-10)).astype(np.float32)
+        a_scale = (m * inv).astype(np.float32)
+        recip = (np.float32(1.0) / a_scale).astype(np.float32)
+        Aq = np.clip((Ag * recip).astype(np.float32), np.float32(qmin), np.float32(qmax))
+        if cast == "e4m3":
+            Aq = e4m3fn_to_f32(f32_to_e4m3fn(Aq))
+        elif cast is not None:
+            raise ValueError(cast)
+        acc += (_t(Aq) @ _t(B[..., k0:k0 + group]).transpose(-1, -2)) * _t(a_scale)
+    acc = acc * float(np.float32(b_scale))
+    if bias is not None:
+        acc = acc + _t(_f32(bias)).reshape(*B.shape[:-2], 1, B.shape[-2])
+    return acc.numpy()
+
+
 def mul_add(G, c_a, c_b):
     """Fused epilogue of the *_mul_add GEMMs: c_a.float() * gemm_out + c_b.float(), in fp32, the
     GEMM result not yet rounded (tests/test_gemm.py:527 and :608;
     kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/test_parity.py:36-38)."""
     return (_f32(c_a) * _f32(G) + _f32(c_b)).astype(np.float32)
+
+
+def split_cat(G, y, S1, S2):
+    """Split-concatenate epilogue of the *_split_cat GEMMs on a GEMM result G [M, D*(S1+S2)] and
+    y [M, D, S3] (kernels/gemm-fused/fused_gemm_a8w8_blockscale_split_cat/test_parity.py:45-56):
+    c1[:, d, :S1] = G[:, d*(S1+S2) : +S1], c2[:, d, :] = the S2 columns behind them, c1[:, d, S1:] = y[:, d, :].
+    Returns (c1 [M, D, S1+S3], c2 [M, D, S2]) in fp32."""
+    G = _f32(G)
+    y = _f32(y)
+    M, D, S3 = y.shape
+    g = G.reshape(M, D, S1 + S2)
+    return np.concatenate([g[:, :, :S1], y], axis=2).astype(np.float32), g[:, :, S1:].astype(np.float32).copy()
 
 
 def rel_err(C, C_ref):

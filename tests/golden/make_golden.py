@@ -19,6 +19,11 @@ Fixtures (all seed 42, the reference tests' seed):
       np.random.seed(42) draws that the test regenerates, checked through a_sum / c_b_sum)
   fused_afp4_mul_add.npz         reference_fp4_gemm_mul_add on generate_test_data()
       kernels/gemm-fused/fused_gemm_afp4wfp4_mul_add/test_parity.py:22-51 (same form)
+  fused_blockscale_split_cat.npz   reference_blockscale_gemm_split_cat
+      kernels/gemm-fused/fused_gemm_a8w8_blockscale_split_cat/test_parity.py:28-57 on seeded integer-valued operands
+      (its D, S1, S2, S3), inputs and outputs
+  gemm_ptgq.npz              reference_torch of kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:40-82
+      (B=4, 128^3, bias; A bf16, int8 weights, scalar weight scale, output bf16)
   e2m1_lut.npz               FP4_LUT / decode_mx_scale of kernels/moe-gemm/moe_op_mxfp4/test_parity.py:30-46
 """
 import argparse
@@ -98,6 +103,23 @@ def main():
     b_codes, b_sc = encode(Bf)
     np.savez_compressed(os.path.join(HERE, "gemm_afp4_batched.npz"), A=a_codes, B=b_codes, a_scales=a_sc,
                         b_scales=b_sc, A_dq=Af.astype(np.float32), B_dq=Bf.astype(np.float32), C_bf16=_bf16_bits(C))
+
+    sc = _load(os.path.join(k, "gemm-fused/fused_gemm_a8w8_blockscale_split_cat/test_parity.py"), "ref_bs_sc")
+    rng = np.random.RandomState(7)
+    a = rng.randint(-8, 9, (64, 256)).astype(np.float32)
+    b = rng.randint(-8, 9, (sc.N, 256)).astype(np.float32)
+    sa = (rng.rand(64, 2) * 0.1 + 0.01).astype(np.float32)
+    sb = (rng.rand(2, sc.N) * 0.1 + 0.01).astype(np.float32)
+    y = rng.randn(64, sc.D, sc.S3).astype(np.float32)
+    c1, c2 = sc.reference_blockscale_gemm_split_cat(a, b, sa, sb, y, sc.GROUP_K, sc.D, sc.S1, sc.S2, sc.S3)
+    np.savez_compressed(os.path.join(HERE, "fused_blockscale_split_cat.npz"), a=a, b=b, a_scale=sa, b_scale=sb, y=y, c1=c1, c2=c2,
+                        D=sc.D, S1=sc.S1, S2=sc.S2, S3=sc.S3)
+
+    pq = _load(os.path.join(k, "gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py"), "ref_ptgq")
+    A, B_int8, b_scale, bias, C = pq.reference_torch()          # A [B,M,K] bf16, B [B,K,N] int8, bias [B,1,N] bf16
+    np.savez_compressed(os.path.join(HERE, "gemm_ptgq.npz"), A_bf16=_bf16_bits(A),
+                        B_nk=B_int8.numpy().transpose(0, 2, 1).copy(), b_scale=np.float32(b_scale.item()),
+                        bias_bf16=_bf16_bits(bias), C_bf16=_bf16_bits(C))
 
     # tests/test_misc.py:522-536 (INT8 per-token), first 64 rows of the 1024x4096 input
     torch.manual_seed(42)

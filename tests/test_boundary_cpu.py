@@ -130,7 +130,8 @@ def test_compute_without_a_gpu_fails_loudly_instead_of_falling_back(lib):
 
 HOT_MODULES = ["quant_tk", "fused_fp8_quant_tk", "fused_mxfp4_quant_tk", "gemm_a8w8_tk", "gemm_a8w8_per_token_scale_tk",
                "gemm_a8w8_blockscale_tk", "gemm_afp4wfp4_tk", "batched_gemm_a8w8_tk", "batched_gemm_afp4wfp4_tk",
-               "fused_gemm_a8w8_blockscale_mul_add_tk", "fused_gemm_afp4wfp4_mul_add_tk", "quant_moe_tk"]
+               "fused_gemm_a8w8_blockscale_mul_add_tk", "fused_gemm_afp4wfp4_mul_add_tk", "quant_moe_tk",
+               "batched_gemm_a8w8_ptgq_tk", "fused_gemm_a8w8_blockscale_split_cat_tk", "fused_gemm_afp4wfp4_split_cat_tk"]
 
 
 def test_loader_discovers_the_reference_module_names(hk):
@@ -154,6 +155,11 @@ def test_functions_and_argument_names_match_the_reference_bindings(hk):
     for mod in (hk.fused_gemm.a8w8_blockscale_mul_add, hk.fused_gemm.afp4wfp4_mul_add):
         assert mod.dispatch.__doc__.startswith(
             "dispatch(a: object, b: object, c: object, a_scale: object, b_scale: object, c_a: object, c_b: object)")
+    d = hk.batched_gemm.a8w8_ptgq.dispatch.__doc__          # kernels/gemm-batched/batched_gemm_a8w8_ptgq/kernel.cpp:241-249
+    assert d.startswith("dispatch(a: object, b: object, b_scale: object, c: object, bias: object")
+    for mod in (hk.fused_gemm.a8w8_blockscale_split_cat, hk.fused_gemm.afp4wfp4_split_cat):
+        assert mod.dispatch.__doc__.startswith(
+            "dispatch(a: object, b: object, a_scale: object, b_scale: object, y: object, c1: object, c2: object)")
     q = hk.moe_routing.quant
     assert q.downcast_to_static_fp8.__doc__.startswith("downcast_to_static_fp8(x: object, y: object, scale: object, M: ")
     assert q.downcast_to_mxfp.__doc__.startswith("downcast_to_mxfp(mx_tensor: object, mx_scale: object, src: object, outer_dim: ")

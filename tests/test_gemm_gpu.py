@@ -316,6 +316,58 @@ def test_unaligned_scale_and_bias_pointers_are_refused(hk):
         hk.batched_gemm.a8w8.dispatch(_dev(aq), _dev(bq), _dev(sa), _dev(sb), C, bias_off)
 
 
+# ---- activation quantizer inside the GEMM's main loop ---------------------------------------------
+
+def _ptgq_case(Bn, M, N, K, seed, with_bias=True):
+    """bf16 activations ~ N(0,1); weights as e4m3 codes of N(0,1) draws scaled into the e4m3 range; a scalar
+    weight scale; bias ~ N(0,1) (distributions of kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:40-52)."""
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(Bn, M, K, generator=g).bfloat16()
+    W = torch.randn(Bn, N, K, generator=g) * 64.0
+    wq = codecs.f32_to_e4m3fn(W.numpy().clip(-448, 448))
+    bias = torch.randn(Bn, 1, N, generator=g).bfloat16() if with_bias else None
+    return A, wq, np.float32(0.05), bias
+
+
+@pytest.mark.parametrize("case", [(4, 128, 128, 128, True),        # the reference's own size (B=4, 128^3, bias)
+                                  (1, 200, 264, 192, False),       # ragged M and N, K = 3 groups (a half-filled stage)
+                                  (2, 384, 512, 1024, True),
+                                  (1, 2048, 4096, 2048, True)])    # several tiles per SM
+def test_batched_gemm_a8w8_ptgq(hk, case):
+    Bn, M, N, K, with_bias = case
+    A, wq, b_scale, bias = _ptgq_case(Bn, M, N, K, seed=61, with_bias=with_bias)
+    C = torch.full((1, Bn, M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    bs = torch.full((1, 1, 1, 1), float(b_scale), device=DEV)
+    hk.batched_gemm.a8w8_ptgq.dispatch(A.to(DEV).view(1, Bn, M, K), _dev(wq).view(1, Bn, N, K), bs, C,
+                                       None if bias is None else bias.to(DEV).view(1, Bn, 1, N))
+    assert hk.last_kernel() == "gemm_fp8_ptgq_kernel"
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = gemm.gemm_ptgq(A.float().numpy(), codecs.e4m3fn_to_f32(wq), b_scale, None if bias is None else bias.float().numpy())
+    _check(C[0], ref, f"ptgq {case}")
+
+
+def test_batched_gemm_a8w8_ptgq_reference_golden(hk, golden_dir):
+    """The reference's own case (its A, bias and scale; its int8 weights clipped to +-16, where every
+    integer is an e4m3 value): the kernel follows the e4m3 oracle to 1e-2 and stays within the
+    quantization noise of the reference's unrounded arithmetic."""
+    g = np.load(os.path.join(golden_dir, "gemm_ptgq.npz"))
+    A = torch.from_numpy(g["A_bf16"].view(np.int16).copy()).view(torch.bfloat16)
+    bias = torch.from_numpy(g["bias_bf16"].view(np.int16).copy()).view(torch.bfloat16)
+    Bc = np.clip(g["B_nk"].astype(np.float32), -16, 16)
+    wq = codecs.f32_to_e4m3fn(Bc)
+    Bn, M, K = A.shape
+    N = Bc.shape[1]
+    C = torch.zeros(Bn, M, N, dtype=torch.bfloat16, device=DEV)
+    bs = torch.full((1,), float(g["b_scale"]), device=DEV)
+    hk.batched_gemm.a8w8_ptgq.dispatch(A.to(DEV), _dev(wq), bs, C, bias.to(DEV))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C, gemm.gemm_ptgq(A.float().numpy(), Bc, g["b_scale"], bias.float().numpy()), "ptgq golden, e4m3 oracle")
+    unrounded = gemm.gemm_ptgq(A.float().numpy(), Bc, g["b_scale"], bias.float().numpy(), qmax=127.0, qmin=-128.0, cast=None)
+    assert gemm.rel_err(C.float().cpu().numpy(), unrounded) < 3e-2
+
+
 # ---- bounded waits -----------------------------------------------------------------------------
 
 def test_bounded_wait_gives_up_by_itself_and_the_device_stays_usable(hk):
@@ -675,6 +727,62 @@ def test_fused_mxfp4_mul_add(hk, shape):
     torch.cuda.synchronize()
     _status_ok()
     _check(C, gemm.mul_add(gemm.gemm_mxfp4(ac, wc, asc, wsc), c_a, c_b), f"mxfp4 mul_add {shape}")
+
+
+# ---- split-concatenate epilogue ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,K,D,S1,S2,S3,gn", [(128, 256, 2, 64, 64, 32, 1),        # the reference's sizes
+                                               (200, 512, 3, 128, 64, 16, 128), (384, 256, 4, 96, 32, 0, 1)])
+def test_fused_blockscale_split_cat(hk, M, K, D, S1, S2, S3, gn):
+    N = D * (S1 + S2)
+    if gn == 128 and N % 128:
+        pytest.skip("N must be a multiple of 128 for 128-column scale groups")
+    aq, bq, _, _ = _fp8_operands(M, N, K, seed=71)
+    g = torch.Generator().manual_seed(7)
+    sa = torch.rand(M, K // 128, generator=g) * 0.1 + 0.01
+    sb = torch.rand(K // 128, N // gn, generator=g) * 0.1 + 0.01
+    y = torch.randn(M, D, max(S3, 1), generator=g).bfloat16()[:, :, :S3].contiguous()
+    c1 = torch.full((M, D, S1 + S3), float("nan"), dtype=torch.bfloat16, device=DEV)
+    c2 = torch.full((M, D, S2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.fused_gemm.a8w8_blockscale_split_cat.dispatch(_dev(aq), _dev(bq), _dev(sa), _dev(sb), _dev(y), c1, c2)
+    assert "split_cat" in hk.last_kernel()
+    torch.cuda.synchronize()
+    _status_ok()
+    r1, r2 = gemm.split_cat(gemm.gemm_fp8_blockscale(aq, bq, sa, sb), y, S1, S2)
+    _check(c1[:, :, :S1], r1[:, :, :S1], "split-cat c1 (GEMM part)")
+    _check(c2, r2, "split-cat c2")
+    assert torch.equal(c1[:, :, S1:].cpu(), y)              # the concatenated part is a copy
+
+
+def test_fused_blockscale_split_cat_reference_golden(hk, golden_dir):
+    g = np.load(os.path.join(golden_dir, "fused_blockscale_split_cat.npz"))
+    aq, bq = codecs.f32_to_e4m3fn(g["a"]), codecs.f32_to_e4m3fn(g["b"])        # integers up to 8: exact in e4m3
+    assert np.array_equal(codecs.e4m3fn_to_f32(aq), g["a"])
+    y = torch.from_numpy(g["y"]).bfloat16()
+    M, D, S1, S2, S3 = g["a"].shape[0], int(g["D"]), int(g["S1"]), int(g["S2"]), int(g["S3"])
+    c1 = torch.zeros(M, D, S1 + S3, dtype=torch.bfloat16, device=DEV)
+    c2 = torch.zeros(M, D, S2, dtype=torch.bfloat16, device=DEV)
+    hk.fused_gemm.a8w8_blockscale_split_cat.dispatch(_dev(aq), _dev(bq), _dev(g["a_scale"]), _dev(g["b_scale"]), _dev(y), c1, c2)
+    torch.cuda.synchronize()
+    _check(c1[:, :, :S1], g["c1"][:, :, :S1], "split-cat golden c1")
+    _check(c2, g["c2"], "split-cat golden c2")
+    assert torch.equal(c1[:, :, S1:].cpu(), y)
+
+
+@pytest.mark.parametrize("M,K,D,S1,S2,S3", [(128, 256, 2, 64, 64, 32), (2304, 256, 17, 128, 64, 16)])   # 128-wide and 192-wide tiles
+def test_fused_mxfp4_split_cat(hk, M, K, D, S1, S2, S3):
+    N = D * (S1 + S2)
+    ac, wc, asc, wsc = _mxfp4_operands(M, N, K, seed=72)
+    y = torch.randn(M, D, S3, generator=torch.Generator().manual_seed(3)).bfloat16()
+    c1 = torch.full((M, D, S1 + S3), float("nan"), dtype=torch.bfloat16, device=DEV)
+    c2 = torch.full((M, D, S2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    hk.fused_gemm.afp4wfp4_split_cat.dispatch(_dev(ac), _dev(wc), _dev(asc), _dev(wsc), _dev(y), c1, c2)
+    torch.cuda.synchronize()
+    _status_ok()
+    r1, r2 = gemm.split_cat(gemm.gemm_mxfp4(ac, wc, asc, wsc), y, S1, S2)
+    _check(c1[:, :, :S1], r1[:, :, :S1], "mxfp4 split-cat c1")
+    _check(c2, r2, "mxfp4 split-cat c2")
+    assert torch.equal(c1[:, :, S1:].cpu(), y)
 
 
 def test_fused_mul_add_validates_its_operands(hk):

@@ -195,6 +195,34 @@ def test_fused_afp4_mul_add_golden(golden_dir):
     assert gemm.rel_err(out, g["ref"]) < 1e-5
 
 
+def test_split_cat_golden(golden_dir):
+    """Block-scale GEMM + split-cat oracle against the reference's reference_blockscale_gemm_split_cat()."""
+    g = np.load(os.path.join(golden_dir, "fused_blockscale_split_cat.npz"))
+    G = gemm.gemm_blockscale_f32(g["a"], g["b"], g["a_scale"], g["b_scale"])
+    c1, c2 = gemm.split_cat(G, g["y"], int(g["S1"]), int(g["S2"]))
+    assert c1.shape == g["c1"].shape and c2.shape == g["c2"].shape
+    np.testing.assert_allclose(c1, g["c1"], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(c2, g["c2"], rtol=1e-6, atol=1e-6)
+
+
+def test_gemm_ptgq_golden(golden_dir):
+    """The in-loop re-quantizing GEMM's oracle in the reference's own arithmetic (INT8 range, quantized
+    values not rounded) reproduces the output of the reference's reference_torch(); in the B200 build's
+    arithmetic (e4m3fn range and cast) it stays within the quantization noise of it."""
+    g = np.load(os.path.join(golden_dir, "gemm_ptgq.npz"))
+    A = _bf16_from_bits(g["A_bf16"]).float().numpy()
+    bias = _bf16_from_bits(g["bias_bf16"]).float().numpy()
+    C_ref = _bf16_from_bits(g["C_bf16"])
+    B = g["B_nk"].astype(np.float32)
+    C = gemm.gemm_ptgq(A, B, g["b_scale"], bias, qmax=127.0, qmin=-128.0, cast=None)
+    assert torch.equal(torch.from_numpy(C).bfloat16(), C_ref)
+    # e4m3 arithmetic on e4m3-representable weights (the same integers clipped to +-16)
+    Bc = np.clip(B, -16, 16)
+    exact = gemm.gemm_ptgq(A, Bc, g["b_scale"], bias, qmax=127.0, qmin=-128.0, cast=None)
+    fp8 = gemm.gemm_ptgq(A, Bc, g["b_scale"], bias)
+    assert 0 < gemm.rel_err(fp8, exact) < 3e-2
+
+
 def test_group32_gemm_with_power_of_two_scales_is_the_mxfp4_gemm(golden_dir):
     g = _load(golden_dir, "gemm_afp4_batched.npz")
     from oracle.codecs import e8m0_to_f32, unpack_e2m1
