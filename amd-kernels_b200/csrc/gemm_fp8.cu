@@ -99,6 +99,10 @@ struct GemmParams {
     int64_t ldc;               // row pitch of C in elements (N unless the result goes into a slab of a wider matrix)
     __nv_bfloat16* peer[7];    // blockscale, gn = 128 only: further copies of the result (same pitch), e.g. the
     int n_peer;                //   same slab of the other GPUs' matrices, written with plain stores from the epilogue
+    const int32_t* expt_data;  // grouped (MoE) mode (kOut == 3): per M tile (expert | block << 16) or -1; rows of expert e are
+    const int32_t* expt_hist;  //   [expt_offs[e], expt_offs[e] + expt_hist[e]) of A / a_scale / C; B, sb and bias_f32 are per expert
+    const int32_t* expt_offs;
+    const float* bias_f32;     //   [E, N] or null
     __nv_bfloat16* c2;         // split-cat epilogue (kOut == 2): column n = d*(s1+s2) + s of the result goes to
     int sc_s1, sc_s2, sc_s3;   //   C[m, d, s] (row length s1+s3) when s < s1, else to c2[m, d, s-s1] (row length s2)
     uint32_t* status;
@@ -186,6 +190,20 @@ __device__ __forceinline__ __nv_bfloat16* split_cat_ptr(const GemmParams& p, int
     return s < p.sc_s1 ? p.C + rd * (p.sc_s1 + p.sc_s3) + s : p.c2 + rd * p.sc_s2 + (s - p.sc_s1);
 }
 
+// Grouped (MoE) mode: M tile `mt` of the tile list -> its expert, first row and row count.
+struct GroupedTile { int e, row0, rows; bool skip; };
+__device__ __forceinline__ GroupedTile grouped_tile(const GemmParams& p, int mt) {
+    const int ed = __ldg(p.expt_data + mt);
+    GroupedTile g;
+    g.skip = ed < 0;
+    g.e = g.skip ? 0 : (ed & 0xFFFF);
+    const int blk = g.skip ? 0 : (ed >> 16);
+    g.row0 = g.skip ? 0 : __ldg(p.expt_offs + g.e) + blk * BM;
+    g.rows = g.skip ? 0 : min(BM, __ldg(p.expt_hist + g.e) - blk * BM);
+    if (g.rows <= 0 || g.row0 >= p.M) g.skip = true;
+    return g;
+}
+
 // Writes 32 consecutive columns of one output row.  `wide` = rows are 32-byte aligned (N % 16 == 0);
 // otherwise 16-byte stores (N % 8 == 0 is guaranteed).
 __device__ __forceinline__ void store_row32(__nv_bfloat16* crow, int col0, int N, const float* v, bool wide) {
@@ -208,7 +226,9 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
 }
 
 // kOut (block-scale): 0 = plain [M, N] result; 1 = the result also goes to p.n_peer further destinations
-// (the other GPUs' copies of the assembled output; 128-column weight-scale groups only); 2 = split-cat.
+// (the other GPUs' copies of the assembled output; 128-column weight-scale groups only); 2 = split-cat;
+// 3 = grouped (MoE): the M tiles come from a device-side list (expert, block), weights, weight scales and the
+// fp32 bias are per expert, rows of A / C are sorted by expert (128-column weight-scale groups only).
 // VAR (block-scale, 128-column groups, one CTA): bit 0 = the epilogue hands a TMEM buffer back through a
 // shared-memory counter that the MMA thread polls, instead of an mbarrier; bit 1 = the epilogue keeps
 // two TMEM loads in flight.  kScaleChunk = K blocks per chunk of staged scales.
@@ -218,6 +238,8 @@ __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
     using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0, kScaleChunk>;
+    constexpr bool kGrouped = kOut == 3;
+    static_assert(!kGrouped || (kBlockScale && kGn128 && !kPair), "grouped mode: block scales, 128-column groups, one CTA");
     constexpr bool kCntRelease = (VAR & 1) != 0 && kBlockScale && kGn128 && !kPair;
     constexpr bool kTwoLoads = (VAR & 2) != 0;
     static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
@@ -292,6 +314,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int b = t / tiles_per_batch;
                 int mb, nb;
                 tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, mb, nb);
+                int a_row = mb * BM, a_z = b, b_z = b;
+                if constexpr (kGrouped) {
+                    const GroupedTile g = grouped_tile(p, mb);
+                    if (g.skip) continue;
+                    a_row = g.row0; a_z = 0; b_z = g.e;
+                }
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer, p.wait_ns)) { ok = false; break; }
                     const uint32_t sa = smem_base + s * L::kStageBytes;
@@ -306,8 +334,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         tma_load_3d_pair(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN + (int)rank * L::kBRows, b);
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), stage_tx);
-                        tma_load_3d(sa, &tmA, full_bar(s), kb * BK, mb * BM, b);
-                        tma_load_3d(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN, b);
+                        tma_load_3d(sa, &tmA, full_bar(s), kb * BK, a_row, a_z);
+                        tma_load_3d(sa + L::kABytes, &tmB, full_bar(s), kb * BK, nb * BN, b_z);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -323,6 +351,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t uses = 0;          // kCntRelease: times buffer `acc` has been filled so far (same for both when acc == 0)
             bool ok = true;
             for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+                if constexpr (kGrouped) {
+                    int mb, nb;
+                    tile_coords(t, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+                    if (grouped_tile(p, mb).skip) continue;
+                }
                 if (!kBlockScale) {
                     if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
                     tc_fence_after();
@@ -390,6 +423,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int tmb, tnb;
             tile_coords(tile - tb * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, tmb, tnb);
             int r = tmb * TILE_M + (int)rank * BM + row_in_tile;
+            const float* sb_base = p.sb;
+            if constexpr (kGrouped) {
+                const GroupedTile g = grouped_tile(p, tmb);        // never called for a skipped tile
+                r = g.row0 + row_in_tile;
+                sb_base += (int64_t)g.e * kblocks * (p.N / 128);
+            }
             if (r >= p.M) r = p.M - 1;
             const int kb0 = chunk * kScaleChunk;
             const float* src = p.sa + (int64_t)r * kblocks + kb0;
@@ -411,18 +450,38 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int kb = kb0 + lane;
             if (lane < kScaleChunk && kb < kblocks)
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
-                             ::"r"(smem_u32(sb_slots + (size_t)buf * EPI_WARPS * kScaleChunk + lane)), "l"(p.sb + (int64_t)kb * nsb + cg) : "memory");
+                             ::"r"(smem_u32(sb_slots + (size_t)buf * EPI_WARPS * kScaleChunk + lane)), "l"(sb_base + (int64_t)kb * nsb + cg) : "memory");
+        };
+        // grouped mode: the first tile at or after `t` (in this CTA's walk) that the tile list does not mark as empty
+        auto next_live_tile = [&](int t) {
+            if constexpr (kGrouped) {
+                while (t < total_tiles) {
+                    int mb_, nb_;
+                    tile_coords(t, p.m_blks, p.n_blks, GROUP_M, mb_, nb_);
+                    if (!grouped_tile(p, mb_).skip) break;
+                    t += tile_step;
+                }
+            }
+            return t;
         };
         if constexpr (kBlockScale && kGn128) {
-            if (tile0 < total_tiles) stage_scales(0, tile0, 0);
+            const int first = next_live_tile(tile0);
+            if (first < total_tiles) stage_scales(0, first, 0);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+        for (int t = next_live_tile(tile0); t < total_tiles && ok; t = next_live_tile(t + tile_step)) {
             const int b = t / tiles_per_batch;
             int mb, nb;
             tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, kPair ? GROUP_M / 2 : GROUP_M, mb, nb);
-            const int row = mb * TILE_M + (int)rank * BM + row_in_tile;
-            const bool row_ok = row < p.M;
+            int row = mb * TILE_M + (int)rank * BM + row_in_tile;
+            bool row_ok = row < p.M;
+            int expert = 0;
+            if constexpr (kGrouped) {
+                const GroupedTile g = grouped_tile(p, mb);
+                row = g.row0 + row_in_tile;
+                row_ok = row_in_tile < g.rows && row < p.M;
+                expert = g.e;
+            }
             const int col_base = nb * BN + grp * COLS_PER_GROUP;
             __nv_bfloat16* crow = p.C + ((int64_t)b * p.M + (row_ok ? row : 0)) * p.ldc;
 
@@ -479,7 +538,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     __syncwarp();
                     {   // stage the scales that follow this chunk
                         int nt = t, nch = ch + 1;
-                        if (nch == nchunks) { nt = t + tile_step; nch = 0; }
+                        if (nch == nchunks) { nt = next_live_tile(t + tile_step); nch = 0; }
                         if (nt < total_tiles) stage_scales(sbuf ^ 1, nt, nch);
                         asm volatile("cp.async.commit_group;" ::: "memory");
                     }
@@ -559,6 +618,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                         for (int i = 0; i < 8; ++i) { v[2 * i] = acc2[c / 2 + i].x; v[2 * i + 1] = acc2[c / 2 + i].y; }
                         if (p.c_a) mul_add_cols<16>(p.c_a, p.c_b, (int64_t)row * p.N + col_base + c, v);
+                        if constexpr (kGrouped) {
+                            if (p.bias_f32) {
+                                const float4* bp = reinterpret_cast<const float4*>(p.bias_f32 + (int64_t)expert * p.N + col_base + c);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float4 bv = __ldg(bp + i);
+                                    v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
+                                }
+                            }
+                        }
                         if constexpr (kOut == 2) {
                             store_bf16x16(split_cat_ptr(p, row, col_base + c), v);
                         } else {
@@ -632,6 +701,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_after();
         if constexpr (kPair) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
     }
+}
+
+// Grouped (MoE) pre-pass: rows of the token-major activations and their scales copied into expert-sorted order,
+// row r <- token gather[r] / n_act.  One warp per row, 16-byte vectors for the codes.
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const uint8_t* __restrict__ x, const float* __restrict__ xs, const int32_t* __restrict__ gather, int n_act,
+                       uint8_t* __restrict__ xg, float* __restrict__ xsg, int64_t rows, int K, int kblocks, int64_t tokens) {
+    const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    int64_t tok = __ldg(gather + r) / n_act;
+    tok = tok < 0 ? 0 : (tok >= tokens ? tokens - 1 : tok);
+    const uint4* src = reinterpret_cast<const uint4*>(x + tok * K);
+    uint4* dst = reinterpret_cast<uint4*>(xg + r * K);
+    for (int i = lane; i < K / 16; i += 32) dst[i] = __ldg(src + i);
+    for (int i = lane; i < kblocks; i += 32) xsg[r * kblocks + i] = __ldg(xs + tok * kblocks + i);
 }
 
 // dst[r, off + j] = src[r, j] for j < w: the concatenation half of the split-cat epilogues
@@ -715,6 +800,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     kern<<<grid, gemm_threads<BN, kBlockScale>(), L::kDynamic, st>>>(tmA, tmB, p);
     note_kernel(kOut == 1 ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,scatter>" : "gemm_fp8_kernel<128,blockscale,scatter>") :
                 kOut == 2 ? (kGn128 ? "gemm_fp8_kernel<128,blockscale,split_cat>" : "gemm_fp8_kernel<128,blockscale,gn1,split_cat>") :
+                kOut == 3 ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,grouped>" : "gemm_fp8_kernel<128,blockscale,grouped>") :
                 kBlockScale ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale>" : kGn128 ? "gemm_fp8_kernel<128,blockscale>" : "gemm_fp8_kernel<128,blockscale,gn1>")
                             : (BN == 256 ? "gemm_fp8_kernel<256,pts>" : BN == 128 ? "gemm_fp8_kernel<128,pts>" : "gemm_fp8_kernel<64,pts>"));
     return check_launch("gemm_fp8_kernel");
@@ -821,6 +907,59 @@ int hkb_gemm_fp8_blockscale_scatter(const void* A, const void* B, void* const* C
     using namespace hkb;
     HKB_REQUIRE(C_dst && n_dst >= 1 && n_dst <= 8, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale_scatter: 1 to 8 destinations");
     return gemm_fp8_blockscale_impl(A, B, C_dst[0], sa, sb, 128, nullptr, nullptr, M, N, K, stream, ldc, C_dst + 1, n_dst - 1);
+}
+
+int hkb_moe_gemm_fp8_blockscale(const void* X, const void* W, void* Y, const float* X_scale, const float* W_scale,
+                                const float* bias, const int32_t* GatherIndx, const int32_t* ExptHist, const int32_t* ExptOffs,
+                                const int32_t* ExptData, int64_t tokens, int64_t rows, int64_t E, int64_t N, int64_t K,
+                                int64_t grid_m, int64_t n_expts_act, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(X && W && Y && X_scale && W_scale && ExptHist && ExptOffs && ExptData, HKB_ERR_BAD_ARG, "moe_gemm_fp8_blockscale: null pointer");
+    HKB_REQUIRE(tokens >= 1 && rows >= 1 && E >= 1 && E <= 65535 && N >= 128 && K >= 128 && grid_m >= 1 && n_expts_act >= 1 &&
+                rows < (1LL << 31) && tokens < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) && grid_m < (1LL << 24),
+                HKB_ERR_BAD_SHAPE, "moe_gemm_fp8_blockscale: bad problem size");
+    HKB_REQUIRE(K % 128 == 0 && N % 128 == 0, HKB_ERR_BAD_SHAPE, "moe_gemm_fp8_blockscale: K and N must be multiples of 128 (the scale group)");
+    HKB_REQUIRE(GatherIndx || tokens == rows, HKB_ERR_BAD_SHAPE, "moe_gemm_fp8_blockscale: without GatherIndx X holds one row per output row");
+    HKB_REQUIRE(aligned16(X) && aligned16(W) && aligned32(Y) && (!bias || aligned16(bias)), HKB_ERR_BAD_ALIGN,
+                "moe_gemm_fp8_blockscale: X, W and bias must be 16-byte, Y 32-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int kblocks = (int)(K / 128);
+    const void* A = X;
+    const float* sa = X_scale;
+    int rc;
+    if (GatherIndx) {
+        // expert-sorted copy of the activations and their scales (per-stream scratch), so that a tile's rows are contiguous for TMA
+        void *xg = nullptr, *xsg = nullptr;
+        rc = scratch_get(SCRATCH_SFA, st, (size_t)rows * K, &xg);
+        if (rc != HKB_OK) return rc;
+        rc = scratch_get(SCRATCH_SFB, st, (size_t)rows * kblocks * 4, &xsg);
+        if (rc != HKB_OK) return rc;
+        moe_gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const uint8_t*)X, X_scale, GatherIndx, (int)n_expts_act,
+                                                                             (uint8_t*)xg, (float*)xsg, rows, (int)K, kblocks, tokens);
+        rc = check_launch("moe_gather_rows_kernel");
+        if (rc != HKB_OK) return rc;
+        A = xg;
+        sa = (const float*)xsg;
+    }
+    GemmParams p{};
+    p.M = (int)rows; p.N = (int)N; p.K = (int)K; p.batch = 1;
+    p.sa = sa; p.sb = W_scale; p.C = (__nv_bfloat16*)Y; p.gn = 128;
+    p.ldc = N; p.wait_ns = kWaitLimitNs; p.skip_kblock = -1;
+    p.expt_data = ExptData; p.expt_hist = ExptHist; p.expt_offs = ExptOffs; p.bias_f32 = bias;
+    rc = status_word(&p.status);
+    if (rc != HKB_OK) return rc;
+    p.m_blks = (int)grid_m;
+    p.a_box_rows = BM;
+    const int sms = sm_count();
+    const int bn = (N % 256 == 0 && grid_m * (N / 256) >= 2LL * sms) ? 256 : 128;
+    p.n_blks = (int)(N / bn);
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)rows, 1, BM);
+    if (rc != HKB_OK) return rc;
+    rc = make_tmap_bytes(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)bn);
+    if (rc != HKB_OK) return rc;
+    if (bn == 256) return launch_gemm<256, 3, true, true, BM, 3>(tmA, tmB, p, st);
+    return launch_gemm<128, 5, true, true, BM, 3>(tmA, tmB, p, st);
 }
 
 int hkb_gemm_fp8_blockscale_split_cat(const void* A, const void* B, const float* sa, const float* sb, int64_t gn,

@@ -484,6 +484,62 @@ SplitDims split_dims(const TView& y, const TView& c1, const TView& c2, int64_t M
     check(hkb_gemm_mxfp4_split_cat(A.ptr, B.ptr, sfa.ptr, sfb.ptr, y.ptr, c1.ptr, c2.ptr, M, N, K, d.S1, d.S2, d.S3, L.stream));
 }
 
+// moe_op_gemm_a8w8_blockscale_tk.moe_a8w8_blockscale(...): kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/kernel.cpp:201-246
+// and :248-282 -- same name, argument names and order, the stride arguments included.  The strides are
+// checked, not used: activations and outputs row-major, weights K-contiguous per output column
+// (W viewed as [E, K, N] with stride_wk == 1, i.e. stored [E, N, K] like every other GEMM operand here).
+[[maybe_unused]] void moe_a8w8_blockscale(py::object X_, py::object W_, py::object Y_, py::object Xs_, py::object Ws_, py::object bias_,
+                                          py::object gather_, py::object hist_, py::object offs_, py::object data_,
+                                          int64_t N, int64_t K, int64_t group_k, int64_t group_n, int64_t grid_m, int64_t grid_n,
+                                          int64_t n_expts_act, int64_t stride_ym, int64_t stride_yn, int64_t stride_xm, int64_t stride_xk,
+                                          int64_t stride_we, int64_t stride_wk, int64_t stride_wn, int64_t stride_xsm, int64_t stride_xsk,
+                                          int64_t stride_wse, int64_t stride_wsk, int64_t stride_wsn) {
+    (void)grid_n;       // the tile width is chosen here
+    // W is the one tensor that may arrive as a non-contiguous view ([E, K, N] over [E, N, K] storage)
+    TView W;
+    {
+        W.none = false;
+        W.name = "W";
+        W.ptr = reinterpret_cast<void*>(W_.attr("data_ptr")().cast<uint64_t>());
+        for (auto d : W_.attr("shape").cast<py::tuple>()) { W.shape.push_back(d.cast<int64_t>()); W.numel *= W.shape.back(); }
+        W.dtype = py::str(W_.attr("dtype")).cast<std::string>();
+        auto dot = W.dtype.rfind('.');
+        if (dot != std::string::npos) W.dtype = W.dtype.substr(dot + 1);
+        py::object dev = W_.attr("device");
+        if (py::str(dev.attr("type")).cast<std::string>() == "cuda") W.device = dev.attr("index").is_none() ? 0 : dev.attr("index").cast<int>();
+    }
+    TView X = view(X_, "X"), Y = view(Y_, "Y"), Xs = view(Xs_, "X_scale"), Ws = view(Ws_, "W_scale"), bias = view(bias_, "bias", true),
+          gather = view(gather_, "GatherIndx", true), hist = view(hist_, "ExptHist"), offs = view(offs_, "ExptOffs"), data = view(data_, "ExptData");
+    want_dtype(X, "X", {"float8_e4m3fn", "uint8"});
+    want_dtype(W, "W", {"float8_e4m3fn", "uint8"});
+    want_dtype(Y, "Y", {"bfloat16"});
+    want_dtype(Xs, "X_scale", {"float32"});
+    want_dtype(Ws, "W_scale", {"float32"});
+    if (!bias.none) want_dtype(bias, "bias", {"float32"});
+    for (const TView* t : {&gather, &hist, &offs, &data})
+        if (!t->none) want_dtype(*t, t->name, {"int32"});
+    if (group_k != 128 || group_n != 128) fail("group_k and group_n must be 128 (the block-scale granularity of this build)");
+    if (X.rank() != 2 || X.dim(1) != K || Y.rank() != 2 || Y.dim(1) != N) fail("X must be [tokens, K] and Y [rows, N]");
+    const int64_t tokens = X.dim(0), rows = Y.dim(0), E = hist.numel;
+    if (W.numel != E * N * K) fail("W must hold E*N*K codes");
+    if (stride_xk != 1 || stride_xm != K || stride_yn != 1 || stride_ym != N) fail("X and Y must be row-major and contiguous");
+    if (stride_wk != 1 || stride_wn != K || stride_we != N * K)
+        fail("W must be K-contiguous per output column: store the weights as [E, N, K] and pass the [E, K, N] view "
+             "(stride_we = N*K, stride_wk = 1, stride_wn = K)");
+    const int64_t kb = K / 128, nb = N / 128;
+    if (Xs.numel != tokens * kb || stride_xsk != 1 || stride_xsm != kb) fail("X_scale must be contiguous [tokens, K/128]");
+    if (Ws.numel != E * kb * nb || stride_wsn != 1 || stride_wsk != nb || stride_wse != kb * nb) fail("W_scale must be contiguous [E, K/128, N/128]");
+    if (!bias.none && bias.numel != E * N) fail("bias must be [E, N]");
+    if (offs.numel != E) fail("ExptOffs must have one entry per expert");
+    if (data.numel < grid_m) fail("ExptData must have grid_m entries");
+    if (!gather.none && gather.numel < rows) fail("GatherIndx must have one entry per output row");
+    same_device({&X, &W, &Y, &Xs, &Ws, &bias, &gather, &hist, &offs, &data});
+    Launch L(X.device);
+    check(hkb_moe_gemm_fp8_blockscale(X.ptr, W.ptr, Y.ptr, (const float*)Xs.ptr, (const float*)Ws.ptr, bias.none ? nullptr : (const float*)bias.ptr,
+                                      gather.none ? nullptr : (const int32_t*)gather.ptr, (const int32_t*)hist.ptr, (const int32_t*)offs.ptr,
+                                      (const int32_t*)data.ptr, tokens, rows, E, N, K, grid_m, n_expts_act, L.stream));
+}
+
 // quant_moe_tk: kernels/moe-misc/quant_moe/kernel.cpp:392-476 (same names, argument order and the
 // redundant integer size arguments, which are checked against the tensors).
 [[maybe_unused]] void downcast_to_static_fp8(py::object x_, py::object y_, py::object scale_, int64_t M, int64_t N) {
@@ -582,6 +638,12 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
 #elif defined(HKB_SHIM_FUSED_GEMM_AFP4WFP4_SPLIT_CAT)
     m.doc() = "MXFP4 x MXFP4 GEMM with the split-concatenate epilogue, sm_100a tcgen05";
     m.def("dispatch", &dispatch_mxfp4_split_cat, "a"_a, "b"_a, "a_scale"_a, "b_scale"_a, "y"_a, "c1"_a, "c2"_a);
+#elif defined(HKB_SHIM_MOE_OP_GEMM_A8W8_BLOCKSCALE)
+    m.doc() = "MoE grouped block-scale FP8 GEMM over expert-sorted rows, sm_100a tcgen05";
+    m.def("moe_a8w8_blockscale", &moe_a8w8_blockscale, "X"_a, "W"_a, "Y"_a, "X_scale"_a, "W_scale"_a, "bias"_a, "GatherIndx"_a,
+          "ExptHist"_a, "ExptOffs"_a, "ExptData"_a, "N"_a, "K"_a, "group_k"_a, "group_n"_a, "grid_m"_a, "grid_n"_a, "n_expts_act"_a,
+          "stride_ym"_a, "stride_yn"_a, "stride_xm"_a, "stride_xk"_a, "stride_we"_a, "stride_wk"_a, "stride_wn"_a,
+          "stride_xsm"_a, "stride_xsk"_a, "stride_wse"_a, "stride_wsk"_a, "stride_wsn"_a);
 #elif defined(HKB_SHIM_QUANT_MOE)
     m.doc() = "MoE casts: static FP8 down-cast, MX (e4m3 / e2m1 + exponent byte per 32) down- and up-cast, sm_100a";
     m.def("downcast_to_static_fp8", &downcast_to_static_fp8, "x"_a, "y"_a, "scale"_a, "M"_a, "N"_a);

@@ -198,6 +198,21 @@ class _FusedGemmNamespace:
     afp4wfp4_a16w16 = _SubModule("fused_gemm_afp4wfp4_a16w16_tk")
 
 
+class _MoeGemmNamespace:
+    # grouped (per-expert) quantized GEMMs over expert-sorted rows
+    a8w8_blockscale = _SubModule("moe_op_gemm_a8w8_blockscale_tk")
+    # names kept for compatibility; not built here (bf16 / int4 / fused-activation variants)
+    gemm = _SubModule("moe_op_tk")
+    e2e = _SubModule("moe_op_e2e_tk")
+    gelu = _SubModule("moe_op_gelu_tk")
+    silu_fused = _SubModule("moe_op_silu_fused_tk")
+    a4w4 = _SubModule("moe_op_gemm_a4w4_tk")
+    a8w4 = _SubModule("moe_op_gemm_a8w4_tk")
+    a8w8 = _SubModule("moe_op_gemm_a8w8_tk")
+    mxfp4 = _SubModule("moe_op_mxfp4_tk")
+    mxfp4_silu_fused = _SubModule("moe_op_mxfp4_silu_fused_tk")
+
+
 class _MoeRoutingNamespace:
     # the MoE activation / weight casts (static FP8, MX FP8 / FP4 down- and up-cast)
     quant = _SubModule("quant_moe_tk")
@@ -212,6 +227,7 @@ class _MoeRoutingNamespace:
 gemm = _GemmNamespace()
 batched_gemm = _BatchedGemmNamespace()
 fused_gemm = _FusedGemmNamespace()
+moe_gemm = _MoeGemmNamespace()
 moe_routing = _MoeRoutingNamespace()
 
 from . import sharded  # noqa: E402,F401  (N-sharded block-scale GEMM over torch.distributed)

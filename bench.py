@@ -19,6 +19,7 @@ synthetic tensors, there is no dataset behind this metric):
   c1   per-token FP8, M=128 N=1024 K=1024 (latency-bound parity configuration)
   p8k  per-token FP8, M=N=K=8192 (tuning shape, not a benchmark configuration)
   p2   per-token FP8 on config 2's shape (tuning shape: isolates the block-scale promotion cost)
+  ptgq bf16 activations quantized per row and 64-wide K group inside the GEMM, scalar weight scale, on config 2's shape
   qbw-fp8 / qbw-1x128 / qbw-mxfp4 / qbw-mxfp4-16k   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192, 16384x8192)
   peak-fp8 / peak-fp4   tensor-core ceiling probe: back-to-back tcgen05.mma on resident operands, all SMs
 
@@ -58,6 +59,7 @@ WORKLOADS = {
     "c5": ("blockscale", 1, 16384, 57344, 8192),
     "p8k": ("pts", 1, 8192, 8192, 8192),
     "p2": ("pts", 1, 4096, 14336, 4096),
+    "ptgq": ("ptgq", 1, 4096, 14336, 4096),
     "qbw-fp8": ("quant-fp8", 1, 16384, 0, 8192),
     "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
     "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),
@@ -246,6 +248,11 @@ class Workload:
             hk.per_token_quant_fwd(W.view(-1, K), self.Wq.view(-1, K), self.sw)
             self.Aq = torch.empty(ashape, dtype=torch.uint8, device=dev)
             self.sa = torch.empty(B * M, 1, dtype=torch.float32, device=dev)
+        elif self.kind == "ptgq":
+            W = (torch.randn(wshape, generator=gw, device=dev) * 0.02).bfloat16()
+            self.sw = (W.float().abs().max() / 448.0).reshape(1).contiguous()          # one scale for the whole tensor
+            self.Wq = torch.empty(wshape, dtype=torch.uint8, device=dev)
+            hk.moe_routing.quant.downcast_to_static_fp8(W, self.Wq, self.sw, self.N, K)
         else:  # mxfp4
             W = (torch.randn(wshape, generator=gw, device=dev) * 0.02).bfloat16()
             self.Wq = torch.empty(self.N, K // 2, dtype=torch.uint8, device=dev)
@@ -261,7 +268,7 @@ class Workload:
             self.sa_tc = torch.zeros(mod.sf_tc_bytes(1, M, K), dtype=torch.uint8, device=dev)
         cshape = (M, self.N) if B == 1 else (B, M, self.N)
         self.C = torch.empty(cshape, dtype=torch.bfloat16, device=dev)
-        self.launches_per_step = 2                                      # quantizer + GEMM
+        self.launches_per_step = 1 if self.kind == "ptgq" else 2        # quantizer + GEMM (one fused kernel for ptgq)
         torch.cuda.synchronize()
 
     # -- device-resident step ------------------------------------------------------------
@@ -269,6 +276,8 @@ class Workload:
         hk, K = self.hk, self.K
         if self.kind == "blockscale":
             hk.fused_rmsnorm_fp8_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
+        elif self.kind == "ptgq":
+            self.A_cur = A                       # quantized inside the GEMM
         elif self.kind == "pts":
             hk.per_token_quant_fwd(A.view(-1, K), self.Aq.view(-1, K), self.sa)
         elif self.kind == "mxfp4":
@@ -300,6 +309,8 @@ class Workload:
                 hk.gemm.a8w8_per_token.dispatch(self.Aq, self.Wq, C, self.sa, self.sw)
             else:
                 hk.batched_gemm.a8w8.dispatch(self.Aq, self.Wq, self.sa, self.sw, C, None)
+        elif self.kind == "ptgq":
+            hk.batched_gemm.a8w8_ptgq.dispatch(getattr(self, "A_cur", self.A), self.Wq, self.sw, C, None)
         elif self.kind == "mxfp4":
             hk.gemm.afp4wfp4.dispatch_tc(self.Aq, self.Wq, C, self.sa_tc, self.sw_tc, True, True)
 
@@ -584,6 +595,10 @@ def cpu_reference_step(name, sample_rows):
                 st["Wq"], st["sw"] = oquant.quant_fp8_128x128(W)
             elif kind == "pts":
                 st["Wq"], st["sw"] = oquant.quant_fp8_per_token(W)
+            elif kind == "ptgq":
+                from oracle import codecs
+                sw = np.float32(W.float().abs().max().item() / 448.0)
+                st["Wq"], st["sw"] = codecs.e4m3fn_to_f32(codecs.f32_to_e4m3fn((W.float().numpy() / sw).clip(-448, 448))), sw
             else:
                 st["Wq"], st["sw"] = oquant.quant_mxfp4(W)
         cpu_reference_step.cache[key] = st
@@ -595,6 +610,8 @@ def cpu_reference_step(name, sample_rows):
     elif kind == "pts":
         aq, sa = oquant.quant_fp8_per_token(A)
         C = ogemm.gemm_fp8_per_token(aq.reshape(B, Ms, K), st["Wq"].reshape(B, N, K), sa.reshape(B, Ms), st["sw"].reshape(B, N))
+    elif kind == "ptgq":
+        C = ogemm.gemm_ptgq(A.float().numpy(), st["Wq"], st["sw"])
     elif kind == "mxfp4":
         aq, sa = oquant.quant_mxfp4(A)
         C = ogemm.gemm_mxfp4(aq, st["Wq"], sa, st["sw"])

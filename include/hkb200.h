@@ -223,6 +223,25 @@ int hkb_gemm_mxfp4_split_cat(const void* A, const void* B, const void* sfa, cons
                              const void* y, void* c1, void* c2, int64_t M, int64_t N, int64_t K,
                              int64_t S1, int64_t S2, int64_t S3, void* stream);
 
+/* Grouped (MoE) block-scale FP8 GEMM: output row r (rows sorted by expert) is
+ *   Y[r, n] = bf16( sum_kb (X[tok(r), kb] @ W[e, n, kb]) * X_scale[tok(r), kb] * W_scale[e, kb, n/128] + bias[e, n] )
+ * with tok(r) = GatherIndx[r] / n_expts_act (GatherIndx NULL: tok(r) = r) and e the expert of r's tile.
+ * X e4m3fn [tokens, K]; W e4m3fn [E, N, K] (K-contiguous, like every GEMM here); Y bf16 [rows, N];
+ * X_scale f32 [tokens, K/128]; W_scale f32 [E, K/128, N/128]; bias f32 [E, N] or NULL; ExptHist[e] rows
+ * of expert e, ExptOffs[e] their first row; ExptData[grid_m]: per 128-row tile (expert | block << 16),
+ * -1 = no tile.  All index arrays int32 in device memory.  K, N multiples of 128.  With GatherIndx the
+ * rows are first copied into expert-sorted order in per-(device, stream) scratch (allocated on first
+ * use).  Replaces moe_a8w8_blockscale(X, W, Y, X_scale, W_scale, bias, GatherIndx, ExptHist, ExptOffs,
+ * ExptData, N, K, group_k, group_n, grid_m, grid_n, n_expts_act, strides...):
+ *   kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/kernel.cpp:26-176,201-246
+ * for group_k = group_n = 128 and e4m3fn codes instead of int8. */
+int hkb_moe_gemm_fp8_blockscale(const void* X, const void* W, void* Y, const float* X_scale,
+                                const float* W_scale, const float* bias_or_null,
+                                const int32_t* GatherIndx_or_null, const int32_t* ExptHist,
+                                const int32_t* ExptOffs, const int32_t* ExptData, int64_t tokens,
+                                int64_t rows, int64_t E, int64_t N, int64_t K, int64_t grid_m,
+                                int64_t n_expts_act, void* stream);
+
 /* quant_moe_tk: wire formats of the MoE activation/weight casts.  Replace
  *   quant_moe_tk.downcast_to_static_fp8(x, y, scale, M, N)
  *   quant_moe_tk.downcast_to_mxfp(mx_tensor, mx_scale, src, outer_dim, quant_dim, is_fp4)

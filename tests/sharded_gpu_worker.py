@@ -1,7 +1,7 @@
 """Worker of tests/test_sharded_gpu.py: one process per GPU under torchrun (NCCL).  Every rank builds the
 same seeded problem, runs the column-sharded block-scale GEMM in its three output forms and compares
-with the single-GPU GEMM of the whole problem computed on its own device.  Prints one JSON line per
-rank; exits non-zero on any mismatch."""
+with the single-GPU GEMM of the whole problem computed on its own device.  Writes rank<r>.json into
+$HKB_TEST_OUT; exits non-zero on any mismatch."""
 import json
 import os
 import sys
@@ -76,7 +76,9 @@ def main():
 
     torch.cuda.synchronize()
     ok = all(v for k, v in out.items() if k.endswith("_ok") or k == "shard_equals_full_slice")
-    print(json.dumps(out), flush=True)
+    # one file per rank: the ranks' stdout shares a pipe and lines can interleave
+    with open(os.path.join(os.environ["HKB_TEST_OUT"], f"rank{rank}.json"), "w") as f:
+        json.dump(out, f)
     dist.barrier()
     dist.destroy_process_group()
     return 0 if ok else 1
