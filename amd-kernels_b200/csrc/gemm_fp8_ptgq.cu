@@ -10,9 +10,13 @@
 //   warp 0        TMA producer of the weight tiles (256 rows x 128 bytes per stage)
 //   warp 1        TMEM allocator + MMA issuer: two tcgen05.mma (K = 32) per 64-K group into one of two
 //                 TMEM buffers, one commit per group
-//   warps 4-7     converter: thread r owns row r of the tile; it reads the row's 64 bf16 of a group
-//                 straight from global memory (one 128-byte line, prefetched one group ahead), takes
-//                 the amax, converts to e4m3 and writes the codes into the operand tile of the stage
+//   warp 2        TMA producer of the bf16 activations: one 128-row x 64-element box (128-byte rows,
+//                 128-byte swizzle) per group into a ring of four slots, so that several groups are in
+//                 flight (a converter that fetched its row from global memory itself, one group ahead,
+//                 was bound by the round trip: 1230 clocks per group)
+//   warps 4-7     converter: thread r owns row r of the tile; it reads the row's 64 bf16 of a group from
+//                 the ring (the swizzle makes the 16-byte reads of neighbouring rows hit different banks),
+//                 takes the amax, converts to e4m3 and writes the codes into the operand tile of the stage
 //                 in the 128-byte-swizzle layout the tensor core reads; the group's scale goes into a
 //                 ring in shared memory for the epilogue
 //   warps 8-15    epilogue: promote every group's partial product from TMEM with the row's scale
@@ -32,7 +36,8 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BKS = 128;             // K per stage (bytes of e4m3 = one swizzle row)
 constexpr int GK = 64;               // K per quantization group
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
+constexpr int ASLOTS = 4;            // ring of bf16 activation groups (16 KB each)
 constexpr int GROUP_M = 8;
 constexpr int RING = 16;             // scale ring, in groups: the converter runs at most 2*STAGES + 2 groups ahead of the epilogue
 constexpr int THREADS = 512;
@@ -51,10 +56,12 @@ struct Smem {
     static constexpr int kABytes = BM * BKS;          // 16 KB of codes
     static constexpr int kBBytes = BN * BKS;          // 32 KB
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kRingOffset = STAGES * kStageBytes;
+    static constexpr int kASlotBytes = BM * GK * 2;   // 16 KB of bf16
+    static constexpr int kASlotOffset = STAGES * kStageBytes;
+    static constexpr int kRingOffset = kASlotOffset + ASLOTS * kASlotBytes;
     static constexpr int kRingBytes = RING * BM * 4;
     static constexpr int kBarOffset = kRingOffset + kRingBytes;
-    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kNumBars = 2 * STAGES + 4 + 2 * ASLOTS;
     static constexpr int kDynamic = kBarOffset + kNumBars * 8 + 16 + 1024;
     static_assert(kDynamic <= 232448, "shared memory budget");
 };
@@ -77,7 +84,7 @@ __device__ __forceinline__ uint2 quant8(const uint4& v, float2 r2) {
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmB, const PtgqParams p) {
+gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PtgqParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -86,6 +93,8 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmB, const PtgqParams p
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto afull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 4 + a); };
+    auto aempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 4 + ASLOTS + a); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::kBarOffset + Smem::kNumBars * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* const ring = reinterpret_cast<float*>(smem + Smem::kRingOffset);      // [RING][BM]
@@ -104,6 +113,10 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmB, const PtgqParams p
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), 8);
+        }
+        for (int a = 0; a < ASLOTS; ++a) {
+            mbar_init(afull_bar(a), 1);
+            mbar_init(aempty_bar(a), 4);      // the four converter warps
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -167,6 +180,26 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmB, const PtgqParams p
                     }
                 }
             }
+        } else if (warp == 2) {
+            // ================= TMA producer (bf16 activations, one 64-K group per slot) =================
+            if (elect_one()) {
+                prefetch_tmap(&tmA);
+                int a = 0;
+                uint32_t aph = 0;
+                bool ok = true;
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                    const int b = t / tiles_per_batch;
+                    int mb, nb;
+                    tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+                    for (int g = 0; g < 2 * kstages; ++g) {
+                        if (!mbar_wait(aempty_bar(a), aph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
+                        mbar_arrive_expect_tx(afull_bar(a), Smem::kASlotBytes);
+                        // x in bytes of the bf16 row; a group past K (odd number of groups) reads as zeros
+                        tma_load_3d(smem_base + Smem::kASlotOffset + a * Smem::kASlotBytes, &tmA, afull_bar(a), g * GK * 2, mb * BM, b);
+                        if (++a == ASLOTS) { a = 0; aph ^= 1; }
+                    }
+                }
+            }
         }
     } else if (warp < 8) {
         // ================= converter: bf16 rows -> e4m3 operand tile + scales =================
@@ -176,46 +209,42 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmB, const PtgqParams p
         const float kInv448 = 1.0f / 448.0f;
         int s = 0;
         uint32_t ph = 0;
+        int a = 0;
+        uint32_t aph = 0;
         uint32_t gg = 0;                                // groups converted so far by this CTA
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            const int b = t / tiles_per_batch;
-            int mb, nb;
-            tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
-            const int row = mb * BM + r;
-            const bool live = row < p.M;
-            const __nv_bfloat16* arow = p.A + ((int64_t)b * p.M + (live ? row : 0)) * p.K;
-            const int kgroups = p.K / GK;
-            // group `gi` of this row: 64 bf16 = four 32-byte loads (zeros past the row or past K)
-            auto load_group = [&](int gi, Wide (&v)[4]) {
-                const bool in = live && gi < kgroups;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = in ? ld_stream32(arow + (int64_t)gi * GK + j * 16) : wide_zero();
-            };
-            Wide cur[4], nxt[4];
-            load_group(0, cur);
             for (int ks = 0; ks < kstages && ok; ++ks) {
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer))) { ok = false; break; }
                 uint8_t* const arow_s = smem + s * Smem::kStageBytes + r * 128;
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    load_group(2 * ks + g + 1, nxt);       // next group in flight while this one is converted
-                    __nv_bfloat162 mx = __hmax2(__hmax2(amax16_packed(cur[0]), amax16_packed(cur[1])),
-                                                __hmax2(amax16_packed(cur[2]), amax16_packed(cur[3])));
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(afull_bar(a), aph, abort_flag, p.status, kErrWaitProducer))) { ok = false; break; }
+                    const uint8_t* src = smem + Smem::kASlotOffset + a * Smem::kASlotBytes + r * 128;
+                    uint4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const uint4*>(src + (((uint32_t)j ^ sw) * 16));
+                    __nv_bfloat162 mx = amax8_packed(v[0]);
+#pragma unroll
+                    for (int j = 1; j < 8; ++j) mx = __hmax2(mx, amax8_packed(v[j]));
                     const float m = fmaxf(hmax_halves(mx), 1e-10f);
                     const float a_scale = m * kInv448;
                     const float recip = __fdiv_rn(1.0f, a_scale);
                     const float2 r2 = make_float2(recip, recip);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint2 lo = quant8(cur[j].lo, r2), hi = quant8(cur[j].hi, r2);
+                        const uint2 lo = quant8(v[2 * j], r2), hi = quant8(v[2 * j + 1], r2);
                         const uint32_t chunk = (uint32_t)(4 * g + j) ^ sw;
                         *reinterpret_cast<uint4*>(arow_s + chunk * 16) = make_uint4(lo.x, lo.y, hi.x, hi.y);
                     }
                     ring[((gg + g) % RING) * BM + r] = a_scale;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+                    // The slot goes back to the TMA producer only now that every value read from it has been
+                    // consumed: an arrive issued right behind the loads let the refill overtake them.
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(aempty_bar(a));
+                    if (++a == ASLOTS) { a = 0; aph ^= 1; }
                 }
+                if (!ok) break;
                 gg += 2;
                 fence_proxy_async_smem();                  // the tensor core reads these generic-proxy writes
                 __syncwarp();
@@ -321,8 +350,8 @@ extern "C" int hkb_gemm_fp8_ptgq(const void* A, const void* B, const float* b_sc
     HKB_REQUIRE(K % GK == 0, HKB_ERR_BAD_SHAPE, "gemm_fp8_ptgq: K=%lld must be a multiple of %d", (long long)K, GK);
     HKB_REQUIRE(N % 8 == 0, HKB_ERR_BAD_SHAPE, "gemm_fp8_ptgq: N=%lld must be a multiple of 8", (long long)N);
     HKB_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) && batch < 65536, HKB_ERR_BAD_SHAPE, "gemm_fp8_ptgq: dimension too large");
-    HKB_REQUIRE(aligned32(A) && aligned16(B) && aligned16(C) && (!bias || aligned16(bias)) && ((uintptr_t)b_scale & 3) == 0,
-                HKB_ERR_BAD_ALIGN, "gemm_fp8_ptgq: A must be 32-byte, B, C and bias 16-byte aligned");
+    HKB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && (!bias || aligned16(bias)) && ((uintptr_t)b_scale & 3) == 0,
+                HKB_ERR_BAD_ALIGN, "gemm_fp8_ptgq: A, B, C and bias must be 16-byte aligned");
     PtgqParams p{};
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.m_blks = (int)((M + BM - 1) / BM);
@@ -333,14 +362,16 @@ extern "C" int hkb_gemm_fp8_ptgq(const void* A, const void* B, const float* b_sc
     p.C = (__nv_bfloat16*)C;
     int rc = status_word(&p.status);
     if (rc != HKB_OK) return rc;
-    CUtensorMap tmB;
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, A, (uint64_t)K * 2, (uint64_t)M, (uint64_t)batch, BM);       // bf16 rows as bytes: a box is 64 elements wide
+    if (rc != HKB_OK) return rc;
     rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)batch, BN);
     if (rc != HKB_OK) return rc;
     const int sms = sm_count();
     HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
     HKB_CUDA(cudaFuncSetAttribute(gemm_fp8_ptgq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic));
     const int tiles = p.m_blks * p.n_blks * p.batch;
-    gemm_fp8_ptgq_kernel<<<tiles < sms ? tiles : sms, THREADS, Smem::kDynamic, (cudaStream_t)stream>>>(tmB, p);
+    gemm_fp8_ptgq_kernel<<<tiles < sms ? tiles : sms, THREADS, Smem::kDynamic, (cudaStream_t)stream>>>(tmA, tmB, p);
     note_kernel("gemm_fp8_ptgq_kernel");
     return check_launch("gemm_fp8_ptgq_kernel");
 }

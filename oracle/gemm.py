@@ -7,6 +7,7 @@ Expressions followed:
   mxfp4       kernels/gemm-basic/gemm_afp4wfp4/test_parity.py:30-31 on operands dequantized as
               kernels/moe-gemm/moe_op_mxfp4/test_parity.py:36-46
   batched     tests/test_gemm.py:366-367 (bias added in fp32 before the bf16 store)
+  MoE grouped kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/test_parity.py:58-99
   ptgq        kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:40-82 (in-loop re-quantization)
   metric      tests/test_gemm.py:190-192
 """
@@ -146,6 +147,40 @@ def mul_add(G, c_a, c_b):
     GEMM result not yet rounded (tests/test_gemm.py:527 and :608;
     kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/test_parity.py:36-38)."""
     return (_f32(c_a) * _f32(G) + _f32(c_b)).astype(np.float32)
+
+
+def moe_gemm_blockscale(X, W, x_scale, w_scale, gather, hist, offs, expt_data, n_expts_act, bias=None, block_m=128, group=128):
+    """Grouped (MoE) block-scale GEMM, restating kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/test_parity.py:58-99
+    (device code: kernel.cpp:60-176): for every tile (expert e, block) of the tile list and every row r of that
+    expert, token = gather[r] // n_expts_act (r itself without gather) and
+        Y[r, n] = sum_kg (X[token, kg] @ W[e, n, kg]) * x_scale[token, kg] * w_scale[e, kg, n // group] (+ bias[e, n]).
+    X [tokens, K] and W [E, N, K] are decoded operand values; returns fp32 [rows, N] (rows no tile covers stay 0)."""
+    X = _f32(X)
+    W = _f32(W)
+    xs = _f32(x_scale)
+    ws = _f32(w_scale)
+    E, N, K = W.shape
+    rows = len(gather) if gather is not None else X.shape[0]
+    Y = np.zeros((rows, N), dtype=np.float32)
+    for ed in np.asarray(expt_data).tolist():
+        if ed < 0:
+            continue
+        e, blk = ed & 0xFFFF, ed >> 16
+        M = int(hist[e])
+        r0 = int(offs[e]) + blk * block_m
+        r1 = int(offs[e]) + min(M, (blk + 1) * block_m)
+        if r1 <= r0:
+            continue
+        tok = (np.asarray(gather[r0:r1]) // n_expts_act) if gather is not None else np.arange(r0, r1)
+        acc = torch.zeros(r1 - r0, N, dtype=torch.float32)
+        for kg in range(K // group):
+            ks = slice(kg * group, (kg + 1) * group)
+            part = _t(X[tok][:, ks]) @ _t(W[e][:, ks]).T
+            acc += part * _t(xs[tok, kg])[:, None] * _t(np.repeat(ws[e, kg], group)[:N])[None, :]
+        if bias is not None:
+            acc += _t(_f32(bias)[e])[None, :]
+        Y[r0:r1] = acc.numpy()
+    return Y
 
 
 def split_cat(G, y, S1, S2):

@@ -22,6 +22,8 @@ Fixtures (all seed 42, the reference tests' seed):
   fused_blockscale_split_cat.npz   reference_blockscale_gemm_split_cat
       kernels/gemm-fused/fused_gemm_a8w8_blockscale_split_cat/test_parity.py:28-57 on seeded integer-valued operands
       (its D, S1, S2, S3), inputs and outputs
+  moe_gemm_blockscale.npz    generate_ogs_routing + reference_moe_a8w8_bs of
+      kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/test_parity.py:29-99 (96 tokens, 4 experts, top-2, K=N=256, group 128)
   gemm_ptgq.npz              reference_torch of kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:40-82
       (B=4, 128^3, bias; A bf16, int8 weights, scalar weight scale, output bf16)
   e2m1_lut.npz               FP4_LUT / decode_mx_scale of kernels/moe-gemm/moe_op_mxfp4/test_parity.py:30-46
@@ -114,6 +116,18 @@ def main():
     c1, c2 = sc.reference_blockscale_gemm_split_cat(a, b, sa, sb, y, sc.GROUP_K, sc.D, sc.S1, sc.S2, sc.S3)
     np.savez_compressed(os.path.join(HERE, "fused_blockscale_split_cat.npz"), a=a, b=b, a_scale=sa, b_scale=sb, y=y, c1=c1, c2=c2,
                         D=sc.D, S1=sc.S1, S2=sc.S2, S3=sc.S3)
+
+    mo = _load(os.path.join(k, "moe-gemm/moe_op_gemm_a8w8_blockscale/test_parity.py"), "ref_moe_bs")
+    np.random.seed(42)
+    tokens, E, top_k, Kd, Nd = 96, 4, 2, 256, 256
+    X = np.random.randint(-16, 17, (tokens, Kd)).astype(np.int8)           # integers e4m3 holds exactly
+    Wm = np.random.randint(-16, 17, (E, Kd, Nd)).astype(np.int8)          # the reference's [E, K, N] form
+    xs = (np.random.rand(tokens, Kd // 128).astype(np.float32) * 0.01)
+    wsc = (np.random.rand(E, Kd // 128, Nd // 128).astype(np.float32) * 0.01)
+    hist, offs, gather, expt_data, grid_m = mo.generate_ogs_routing(tokens, E, top_k)
+    Y = mo.reference_moe_a8w8_bs(X, Wm, xs, wsc, gather, hist, offs, expt_data, top_k, 128, 128)
+    np.savez_compressed(os.path.join(HERE, "moe_gemm_blockscale.npz"), X=X, W_nk=Wm.transpose(0, 2, 1).copy(), x_scale=xs,
+                        w_scale=wsc, hist=hist, offs=offs, gather=gather, expt_data=expt_data, top_k=top_k, Y=Y)
 
     pq = _load(os.path.join(k, "gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py"), "ref_ptgq")
     A, B_int8, b_scale, bias, C = pq.reference_torch()          # A [B,M,K] bf16, B [B,K,N] int8, bias [B,1,N] bf16

@@ -131,7 +131,8 @@ def test_compute_without_a_gpu_fails_loudly_instead_of_falling_back(lib):
 HOT_MODULES = ["quant_tk", "fused_fp8_quant_tk", "fused_mxfp4_quant_tk", "gemm_a8w8_tk", "gemm_a8w8_per_token_scale_tk",
                "gemm_a8w8_blockscale_tk", "gemm_afp4wfp4_tk", "batched_gemm_a8w8_tk", "batched_gemm_afp4wfp4_tk",
                "fused_gemm_a8w8_blockscale_mul_add_tk", "fused_gemm_afp4wfp4_mul_add_tk", "quant_moe_tk",
-               "batched_gemm_a8w8_ptgq_tk", "fused_gemm_a8w8_blockscale_split_cat_tk", "fused_gemm_afp4wfp4_split_cat_tk"]
+               "batched_gemm_a8w8_ptgq_tk", "fused_gemm_a8w8_blockscale_split_cat_tk", "fused_gemm_afp4wfp4_split_cat_tk",
+               "moe_op_gemm_a8w8_blockscale_tk"]
 
 
 def test_loader_discovers_the_reference_module_names(hk):

@@ -368,6 +368,88 @@ def test_batched_gemm_a8w8_ptgq_reference_golden(hk, golden_dir):
     assert gemm.rel_err(C.float().cpu().numpy(), unrounded) < 3e-2
 
 
+# ---- grouped (MoE) block-scale GEMM -----------------------------------------------------------------
+
+def _routing(tokens, E, top_k, seed, block_m=128):
+    """Expert-sorted routing tables in the form of kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/test_parity.py:29-58."""
+    rng = np.random.RandomState(seed)
+    assigns = rng.randint(0, E, (tokens, top_k))
+    hist = np.bincount(assigns.ravel(), minlength=E).astype(np.int32)
+    offs = np.concatenate([[0], np.cumsum(hist)[:-1]]).astype(np.int32)
+    order = np.argsort(assigns.ravel(), kind="stable")
+    gather = order.astype(np.int32)                        # flat (token * top_k + k) index of each sorted row
+    tiles = [e | (b << 16) for e in range(E) for b in range((hist[e] + block_m - 1) // block_m)]
+    return hist, offs, gather, np.array(tiles + [-1], dtype=np.int32)      # one empty entry at the end of the tile list
+
+
+def _moe_call(hk, X, W_nk, Y, xs, ws, bias, gather, hist, offs, data, top_k):
+    E, N, K = W_nk.shape
+    kb, nb = K // 128, N // 128
+    hk.moe_gemm.a8w8_blockscale.moe_a8w8_blockscale(
+        X, W_nk.transpose(1, 2), Y, xs, ws, bias, gather, hist, offs, data, N, K, 128, 128, data.numel(), (N + 63) // 64, top_k,
+        N, 1, K, 1, N * K, 1, K, kb, 1, kb * nb, nb, 1)
+
+
+@pytest.mark.parametrize("tokens,E,top_k,K,N,with_bias", [(96, 4, 2, 256, 256, False), (700, 8, 2, 512, 1024, True),
+                                                          (4096, 16, 4, 1024, 4096, True)])      # the last one takes the 256-wide tiles
+def test_moe_gemm_blockscale(hk, tokens, E, top_k, K, N, with_bias):
+    g = torch.Generator().manual_seed(81)
+    X = torch.randn(tokens, K, generator=g).bfloat16()
+    W = (torch.randn(E * N, K, generator=g) * 0.02).bfloat16()
+    xq, xs = quant.quant_fp8_1x128(X)
+    wq = np.empty((E, N, K), dtype=np.uint8); ws = np.empty((E, K // 128, N // 128), dtype=np.float32)
+    for e in range(E):
+        wq[e], ws[e] = quant.quant_fp8_128x128(W[e * N:(e + 1) * N])
+    bias = torch.randn(E, N, generator=g) if with_bias else None
+    hist, offs, gather, data = _routing(tokens, E, top_k, seed=5)
+    rows = tokens * top_k
+    Y = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _moe_call(hk, _dev(xq), _dev(wq), Y, _dev(xs), _dev(ws), None if bias is None else bias.to(DEV), _dev(gather), _dev(hist), _dev(offs),
+              _dev(data), top_k)
+    assert "grouped" in hk.last_kernel()
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = gemm.moe_gemm_blockscale(codecs.e4m3fn_to_f32(xq), codecs.e4m3fn_to_f32(wq), xs, ws, gather, hist, offs, data, top_k,
+                                   None if bias is None else bias.numpy())
+    _check(Y, ref, f"moe blockscale tokens={tokens} E={E}")
+
+
+def test_moe_gemm_blockscale_reference_golden(hk, golden_dir):
+    """The reference's own routing generator and reference function (group 128) on integer operands e4m3 holds exactly."""
+    g = np.load(os.path.join(golden_dir, "moe_gemm_blockscale.npz"))
+    xq = codecs.f32_to_e4m3fn(g["X"].astype(np.float32)); wq = codecs.f32_to_e4m3fn(g["W_nk"].astype(np.float32))
+    rows, N = g["Y"].shape
+    Y = torch.zeros(rows, N, dtype=torch.bfloat16, device=DEV)
+    data = torch.from_numpy(g["expt_data"]).to(DEV)
+    _moe_call(hk, _dev(xq), _dev(wq), Y, _dev(g["x_scale"]), _dev(g["w_scale"]), None, _dev(g["gather"]), _dev(g["hist"]), _dev(g["offs"]),
+              data, int(g["top_k"]))
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(Y, g["Y"], "moe blockscale golden")
+
+
+def test_moe_gemm_blockscale_without_gather_and_layout_check(hk):
+    """GatherIndx=None: X already holds one row per sorted output row; an N-contiguous weight tensor is refused."""
+    tokens, E, K, N = 300, 3, 256, 384
+    g = torch.Generator().manual_seed(82)
+    xq, xs = quant.quant_fp8_1x128(torch.randn(tokens, K, generator=g).bfloat16())
+    wq = np.empty((E, N, K), dtype=np.uint8); ws = np.empty((E, K // 128, N // 128), dtype=np.float32)
+    for e in range(E):
+        wq[e], ws[e] = quant.quant_fp8_128x128((torch.randn(N, K, generator=g) * 0.02).bfloat16())
+    hist = np.array([100, 0, 200], dtype=np.int32); offs = np.array([0, 100, 100], dtype=np.int32)       # an expert without rows
+    data = np.array([0, 2, 2 | (1 << 16)], dtype=np.int32)
+    Y = torch.full((tokens, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _moe_call(hk, _dev(xq), _dev(wq), Y, _dev(xs), _dev(ws), None, None, _dev(hist), _dev(offs), _dev(data), 1)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = gemm.moe_gemm_blockscale(codecs.e4m3fn_to_f32(xq), codecs.e4m3fn_to_f32(wq), xs, ws, None, hist, offs, data, 1)
+    _check(Y, ref, "moe blockscale, no gather")
+    with pytest.raises(RuntimeError, match="K-contiguous"):
+        Wkn = _dev(wq).transpose(1, 2).contiguous()         # physically [E, K, N]
+        hk.moe_gemm.a8w8_blockscale.moe_a8w8_blockscale(_dev(xq), Wkn, Y, _dev(xs), _dev(ws), None, None, _dev(hist), _dev(offs), _dev(data),
+                                                        N, K, 128, 128, 3, 6, 1, N, 1, K, 1, K * N, N, 1, 2, 1, 6, 3, 1)
+
+
 # ---- bounded waits -----------------------------------------------------------------------------
 
 def test_bounded_wait_gives_up_by_itself_and_the_device_stays_usable(hk):

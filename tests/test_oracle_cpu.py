@@ -195,6 +195,14 @@ def test_fused_afp4_mul_add_golden(golden_dir):
     assert gemm.rel_err(out, g["ref"]) < 1e-5
 
 
+def test_moe_gemm_blockscale_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "moe_gemm_blockscale.npz"))
+    Y = gemm.moe_gemm_blockscale(g["X"].astype(np.float32), g["W_nk"].astype(np.float32), g["x_scale"], g["w_scale"], g["gather"],
+                                 g["hist"], g["offs"], g["expt_data"], int(g["top_k"]))
+    np.testing.assert_allclose(Y, g["Y"], rtol=1e-5, atol=1e-6)
+    assert (np.abs(g["Y"]).sum(axis=1) > 0).all()        # every sorted row belongs to a tile
+
+
 def test_split_cat_golden(golden_dir):
     """Block-scale GEMM + split-cat oracle against the reference's reference_blockscale_gemm_split_cat()."""
     g = np.load(os.path.join(golden_dir, "fused_blockscale_split_cat.npz"))
