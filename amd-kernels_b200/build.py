@@ -41,6 +41,7 @@ SHIMS = {
     "fused_gemm_a8w8_blockscale_split_cat_tk": "HKB_SHIM_FUSED_GEMM_A8W8_BLOCKSCALE_SPLIT_CAT",
     "fused_gemm_afp4wfp4_split_cat_tk": "HKB_SHIM_FUSED_GEMM_AFP4WFP4_SPLIT_CAT",
     "moe_op_gemm_a8w8_blockscale_tk": "HKB_SHIM_MOE_OP_GEMM_A8W8_BLOCKSCALE",
+    "moe_op_mxfp4_tk": "HKB_SHIM_MOE_OP_MXFP4",
     "quant_moe_tk": "HKB_SHIM_QUANT_MOE",
 }
 

@@ -41,7 +41,7 @@ int sm_count();
 
 // Per-device, lazily grown scratch owned by the library (freed by hkb_release()).
 // `slot` separates independent users so they do not overwrite each other.
-enum ScratchSlot { SCRATCH_SFA = 0, SCRATCH_SFB = 1, SCRATCH_SLOTS = 2 };
+enum ScratchSlot { SCRATCH_SFA = 0, SCRATCH_SFB = 1, SCRATCH_ROWS = 2, SCRATCH_SLOTS = 3 };
 // Scratch is keyed by (device, stream): calls on different streams of one device get different
 // blocks, so they may overlap on the GPU.  A device keeps blocks for up to kScratchStreams streams;
 // when more streams than that use scratch, the least recently used stream's blocks are recycled

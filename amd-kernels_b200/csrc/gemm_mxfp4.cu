@@ -37,6 +37,14 @@ struct Mxfp4Params {
     __nv_bfloat16* C;
     const __nv_bfloat16* c_a;     // fused multiply-add epilogue C = c_a * (A B^T) + c_b, both [batch, M, N]; null = plain
     const __nv_bfloat16* c_b;
+    // grouped (MoE) mode, one-CTA kernels: M tile mb holds the sorted rows [mb*128, mb*128+128) of expert expert_ids[mb]
+    // (-1: no expert, zeros are written); output row = sorted_ids[row] when < num_valid; B, its scales and b_scale_e per expert
+    const int32_t* expert_ids;    // null = not grouped
+    const int32_t* sorted_ids;
+    int num_valid;
+    const float* topk_w;          // per output row, or null
+    const float* a_scale1;        // one float or null
+    const float* b_scale_e;       // [E] or null
     __nv_bfloat16* c2;            // split-cat epilogue (sc_s1 > 0, one-CTA kernels, batch 1): column n = d*(s1+s2) + s goes to
     int sc_s1, sc_s2, sc_s3;      //   C[m, d, s] (row length s1+s3) when s < s1, else to c2[m, d, s-s1] (row length s2)
     uint32_t* status;
@@ -46,8 +54,11 @@ struct Mxfp4Params {
 // and atoms past K/128 are written as zero bytes (they meet zero-filled operand data).  One CTA
 // moves 128 rows x 32 atoms through shared memory so that both the global reads (128 B per row)
 // and writes (512 B per atom) are coalesced.
+// Row indirection (MoE): with `ids`, row r of the output is source row ids[r] / ids_div when ids[r] < ids_valid and
+// zero otherwise; R then counts output rows.
 __global__ void __launch_bounds__(256)
-sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int R, int katoms, int katoms_pad, int rblks) {
+sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int R, int katoms, int katoms_pad, int rblks,
+                   const int32_t* __restrict__ ids = nullptr, int ids_div = 1, int ids_valid = 0) {
     __shared__ uint32_t tile[32][129];   // [atom in chunk][word in atom], padded
     const int b = blockIdx.z;
     const int rb = blockIdx.y;
@@ -60,7 +71,11 @@ sf_relayout_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, i
         const int r = idx >> 5, a = idx & 31;
         const int row = rb * 128 + r;
         uint32_t v = 0;
-        if (row < R && ka0 + a < katoms) v = __ldg(s32 + (int64_t)row * katoms + ka0 + a);
+        if (row < R && ka0 + a < katoms) {
+            int64_t srow = row;
+            if (ids) { const int id = __ldg(ids + row); srow = id < ids_valid ? id / ids_div : -1; }
+            if (srow >= 0) v = __ldg(s32 + srow * katoms + ka0 + a);
+        }
         tile[a][(r & 31) * 4 + (r >> 5)] = v;
     }
     __syncthreads();
@@ -155,16 +170,21 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int b = t / tiles_per_batch;
                 int mb, nb;
                 tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
+                int bb = b;                                   // batch coordinate of B and its scales: the expert in grouped mode
+                if (p.expert_ids) {
+                    bb = __ldg(p.expert_ids + mb);
+                    if (bb < 0) continue;
+                }
                 const uint8_t* sfa_row = p.sfa + ((int64_t)b * p.sfa_rblks + mb) * p.katoms * 512;
                 // first 128-row scale atom that the tile's B rows touch
                 const int atom0 = (nb * BN) >> 7;
-                const uint8_t* sfb_row = p.sfb + ((int64_t)b * p.sfb_rblks + atom0) * p.katoms * 512;
+                const uint8_t* sfb_row = p.sfb + ((int64_t)bb * p.sfb_rblks + atom0) * p.katoms * 512;
                 for (int ks = 0; ks < kstages; ++ks) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer)) { ok = false; break; }
                     mbar_arrive_expect_tx(full_bar(s), stage_tx);
                     const uint32_t st = smem_base + s * Smem::kStageBytes;
                     tma_load_3d(st, &tmA, full_bar(s), ks * BKB, mb * BM, b);
-                    tma_load_3d(st + Smem::kABytes, &tmB, full_bar(s), ks * BKB, nb * BN, b);
+                    tma_load_3d(st + Smem::kABytes, &tmB, full_bar(s), ks * BKB, nb * BN, bb);
                     bulk_load(st + Smem::kSfaOff, sfa_row + (int64_t)ks * SF_STAGE, SF_STAGE, full_bar(s));
 #pragma unroll
                     for (int r = 0; r < SFB_ATOMS; ++r)
@@ -182,6 +202,11 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint32_t acc_ph = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                if (p.expert_ids) {
+                    int mb_, nb_;
+                    tile_coords(t, p.m_blks, p.n_blks, GROUP_M, mb_, nb_);
+                    if (__ldg(p.expert_ids + mb_) < 0) continue;
+                }
                 if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
@@ -232,8 +257,26 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int b = t / tiles_per_batch;
             int mb, nb;
             tile_coords(t - b * tiles_per_batch, p.m_blks, p.n_blks, GROUP_M, mb, nb);
-            const int row = mb * BM + row_in_tile;
-            const bool row_ok = row < p.M;
+            int row = mb * BM + row_in_tile;
+            bool row_ok = row < p.M;
+            float row_scale = 1.0f;
+            if (p.expert_ids) {
+                // grouped mode: this sorted row's output row and its scale (per-tensor x per-expert x routing weight)
+                const int e = __ldg(p.expert_ids + mb);
+                const int id = row_ok ? __ldg(p.sorted_ids + row) : p.num_valid;
+                row_ok = id < p.num_valid;
+                row = row_ok ? id : 0;
+                if (e < 0) {
+                    // no expert for this block: the rows it names get zeros (nothing was accumulated for them)
+                    if (row_ok) {
+                        for (int c = 0; c < BN; c += 8)
+                            if (nb * BN + c < p.N) *reinterpret_cast<uint4*>(p.C + (int64_t)row * p.N + nb * BN + c) = make_uint4(0, 0, 0, 0);
+                    }
+                    continue;
+                }
+                row_scale = (p.a_scale1 ? __ldg(p.a_scale1) : 1.0f) * (p.b_scale_e ? __ldg(p.b_scale_e + e) : 1.0f);
+                if (p.topk_w && row_ok) row_scale *= __ldg(p.topk_w + id);
+            }
             const int64_t row_off = ((int64_t)b * p.M + (row_ok ? row : 0)) * p.N;
             __nv_bfloat16* crow = p.C + row_off;
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue))) break;
@@ -255,6 +298,10 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                 unpack8(__ldg(reinterpret_cast<const uint4*>(p.c_b + row_off + col0 + j)), cb);
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) r[j + i] = __float_as_uint(__fmaf_rn(ca[i], __uint_as_float(r[j + i]), cb[i]));
+                            }
+                            if (p.expert_ids) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) r[j + i] = __float_as_uint(__uint_as_float(r[j + i]) * row_scale);
                             }
                             uint4 o;
                             __nv_bfloat162 q0 = __floats2bfloat162_rn(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
@@ -536,6 +583,23 @@ int launch_sf_relayout(const void* src, void* dst, int64_t batch, int64_t R, int
     return check_launch("sf_relayout_kernel");
 }
 
+// MoE pre-pass: output row r <- source row ids[r] / div when ids[r] < valid, zeros otherwise.  One warp per row.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ ids, int div, int valid, uint8_t* __restrict__ xg,
+                   int64_t rows, int row_bytes) {
+    const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const int id = __ldg(ids + r);
+    uint4* dst = reinterpret_cast<uint4*>(xg + r * row_bytes);
+    if (id < valid && id >= 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(id / div) * row_bytes);
+        for (int i = lane; i < row_bytes / 16; i += 32) dst[i] = __ldg(src + i);
+    } else {
+        for (int i = lane; i < row_bytes / 16; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+    }
+}
+
 // sfa_tc / sfb_tc: the scale pointer already is in the tensor-core layout (hkb_mxfp4_sf_to_tc or
 // hkb_quant_mxfp4_tc); otherwise it is row-major [batch, rows, K/32] and is re-laid-out into
 // per-(device, stream) scratch first.
@@ -666,6 +730,79 @@ int gemm_mxfp4_impl(const void* A, const void* B, void* C, const void* sfa, cons
 extern "C" int hkb_gemm_mxfp4(const void* A, const void* B, void* C, const void* sfa, const void* sfb,
                               int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
     return hkb::gemm_mxfp4_impl(A, B, C, sfa, sfb, false, false, nullptr, nullptr, batch, M, N, K, stream);
+}
+
+extern "C" int hkb_moe_gemm_mxfp4(const void* A, const void* B, void* C, const void* A_mx_scale, const void* B_mx_scale,
+                                  const float* A_scale, const float* B_scale, const float* topk_weights,
+                                  const int32_t* sorted_token_ids, const int32_t* expert_ids, int64_t tokens, int64_t num_padded,
+                                  int64_t E, int64_t N, int64_t K, int64_t num_valid_tokens, int64_t top_k, int mul_routed_weight,
+                                  void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(A && B && C && A_mx_scale && B_mx_scale && sorted_token_ids && expert_ids, HKB_ERR_BAD_ARG, "moe_gemm_mxfp4: null pointer");
+    HKB_REQUIRE(!mul_routed_weight || topk_weights, HKB_ERR_BAD_ARG, "moe_gemm_mxfp4: mul_routed_weight needs topk_weights");
+    HKB_REQUIRE(tokens >= 1 && num_padded >= 1 && num_padded % BM == 0 && E >= 1 && E < 65536 && top_k >= 1 && num_valid_tokens >= 0 &&
+                num_padded < (1LL << 31) && tokens < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31),
+                HKB_ERR_BAD_SHAPE, "moe_gemm_mxfp4: bad problem size (the sorted row list is padded to multiples of %d)", BM);
+    HKB_REQUIRE(K % 128 == 0 && N % 8 == 0, HKB_ERR_BAD_SHAPE, "moe_gemm_mxfp4: K must be a multiple of 128 and N of 8");
+    HKB_REQUIRE(aligned16(A) && aligned16(B) && aligned16(C) && ((uintptr_t)A_mx_scale & 3) == 0 && ((uintptr_t)B_mx_scale & 3) == 0,
+                HKB_ERR_BAD_ALIGN, "moe_gemm_mxfp4: A, B, C must be 16-byte and the scale arrays 4-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    Mxfp4Params p{};
+    p.M = (int)num_padded; p.N = (int)N; p.K = (int)K; p.batch = 1;
+    p.m_blks = (int)(num_padded / BM);
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
+    const bool wide = (int64_t)p.m_blks * ((N + 191) / 192) >= 2LL * sms;
+    const int bn = wide ? 192 : 128;
+    p.n_blks = (int)((N + bn - 1) / bn);
+    p.sfa_rblks = sf_tc_rblks(num_padded);
+    p.sfb_rblks = sf_tc_rblks(N);
+    p.katoms = sf_tc_katoms(K);
+    p.C = (__nv_bfloat16*)C;
+    p.expert_ids = expert_ids; p.sorted_ids = sorted_token_ids; p.num_valid = (int)num_valid_tokens;
+    p.topk_w = mul_routed_weight ? topk_weights : nullptr;
+    p.a_scale1 = A_scale; p.b_scale_e = B_scale;
+    int rc = status_word(&p.status);
+    if (rc != HKB_OK) return rc;
+    // expert-sorted copy of the activation codes, and both operands' scales in the tensor core's layout (per-stream scratch)
+    void *ag = nullptr, *sfa_sw = nullptr, *sfb_sw = nullptr;
+    rc = scratch_get(SCRATCH_ROWS, st, (size_t)num_padded * (K / 2), &ag);
+    if (rc != HKB_OK) return rc;
+    rc = scratch_get(SCRATCH_SFA, st, (size_t)p.sfa_rblks * p.katoms * 512, &sfa_sw);
+    if (rc != HKB_OK) return rc;
+    rc = scratch_get(SCRATCH_SFB, st, (size_t)E * p.sfb_rblks * p.katoms * 512, &sfb_sw);
+    if (rc != HKB_OK) return rc;
+    gather_rows_kernel<<<(unsigned)((num_padded + 7) / 8), 256, 0, st>>>((const uint8_t*)A, sorted_token_ids, (int)top_k, (int)num_valid_tokens,
+                                                                         (uint8_t*)ag, num_padded, (int)(K / 2));
+    {
+        const int katoms_src = (int)(K / 128);
+        dim3 ga((unsigned)((p.katoms + 31) / 32), (unsigned)p.sfa_rblks, 1);
+        sf_relayout_kernel<<<ga, 256, 0, st>>>((const uint8_t*)A_mx_scale, (uint8_t*)sfa_sw, (int)num_padded, katoms_src, p.katoms, p.sfa_rblks,
+                                               sorted_token_ids, (int)top_k, (int)num_valid_tokens);
+    }
+    rc = check_launch("moe_gemm_mxfp4 pre-pass");
+    if (rc != HKB_OK) return rc;
+    rc = launch_sf_relayout(B_mx_scale, sfb_sw, E, N, K, st);
+    if (rc != HKB_OK) return rc;
+    p.sfa = (const uint8_t*)sfa_sw;
+    p.sfb = (const uint8_t*)sfb_sw;
+    CUtensorMap tmA, tmB;
+    rc = make_tmap_bytes(&tmA, ag, (uint64_t)K / 2, (uint64_t)num_padded, 1, BM);
+    if (rc != HKB_OK) return rc;
+    rc = make_tmap_bytes(&tmB, B, (uint64_t)K / 2, (uint64_t)N, (uint64_t)E, (uint32_t)bn);
+    if (rc != HKB_OK) return rc;
+    const int tiles = p.m_blks * p.n_blks;
+    const int grid = tiles < sms ? tiles : sms;
+    if (wide) {
+        HKB_CUDA(cudaFuncSetAttribute(gemm_mxfp4_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<192>::kDynamic));
+        gemm_mxfp4_kernel<192><<<grid, 192, Cfg<192>::kDynamic, st>>>(tmA, tmB, p);
+        note_kernel("gemm_mxfp4_kernel<192> (grouped)");
+    } else {
+        HKB_CUDA(cudaFuncSetAttribute(gemm_mxfp4_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::kDynamic));
+        gemm_mxfp4_kernel<128><<<grid, 192, Cfg<128>::kDynamic, st>>>(tmA, tmB, p);
+        note_kernel("gemm_mxfp4_kernel<128> (grouped)");
+    }
+    return check_launch("gemm_mxfp4_kernel");
 }
 
 extern "C" int hkb_gemm_mxfp4_split_cat(const void* A, const void* B, const void* sfa, const void* sfb, const void* y,

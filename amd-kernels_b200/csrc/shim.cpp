@@ -34,7 +34,7 @@ struct TView {
 
 [[noreturn]] void fail(const std::string& m) { throw std::runtime_error(m); }
 
-TView view(const py::object& t, const char* name, bool allow_none = false) {
+TView view(const py::object& t, const char* name, bool allow_none = false, bool need_contiguous = true) {
     TView v;
     if (t.is_none()) {
         if (!allow_none) fail(std::string(name) + ": tensor is None");
@@ -51,7 +51,7 @@ TView view(const py::object& t, const char* name, bool allow_none = false) {
         auto dot = v.dtype.rfind('.');
         if (dot != std::string::npos) v.dtype = v.dtype.substr(dot + 1);
     }
-    if (py::hasattr(t, "is_contiguous") && !t.attr("is_contiguous")().cast<bool>())
+    if (need_contiguous && py::hasattr(t, "is_contiguous") && !t.attr("is_contiguous")().cast<bool>())
         fail(std::string(name) + ": tensor must be contiguous (row-major, inner stride 1)");
     v.name = name;
     if (py::hasattr(t, "device")) {
@@ -496,18 +496,7 @@ SplitDims split_dims(const TView& y, const TView& c1, const TView& c2, int64_t M
                                           int64_t stride_wse, int64_t stride_wsk, int64_t stride_wsn) {
     (void)grid_n;       // the tile width is chosen here
     // W is the one tensor that may arrive as a non-contiguous view ([E, K, N] over [E, N, K] storage)
-    TView W;
-    {
-        W.none = false;
-        W.name = "W";
-        W.ptr = reinterpret_cast<void*>(W_.attr("data_ptr")().cast<uint64_t>());
-        for (auto d : W_.attr("shape").cast<py::tuple>()) { W.shape.push_back(d.cast<int64_t>()); W.numel *= W.shape.back(); }
-        W.dtype = py::str(W_.attr("dtype")).cast<std::string>();
-        auto dot = W.dtype.rfind('.');
-        if (dot != std::string::npos) W.dtype = W.dtype.substr(dot + 1);
-        py::object dev = W_.attr("device");
-        if (py::str(dev.attr("type")).cast<std::string>() == "cuda") W.device = dev.attr("index").is_none() ? 0 : dev.attr("index").cast<int>();
-    }
+    TView W = view(W_, "W", false, false);
     TView X = view(X_, "X"), Y = view(Y_, "Y"), Xs = view(Xs_, "X_scale"), Ws = view(Ws_, "W_scale"), bias = view(bias_, "bias", true),
           gather = view(gather_, "GatherIndx", true), hist = view(hist_, "ExptHist"), offs = view(offs_, "ExptOffs"), data = view(data_, "ExptData");
     want_dtype(X, "X", {"float8_e4m3fn", "uint8"});
@@ -538,6 +527,50 @@ SplitDims split_dims(const TView& y, const TView& c1, const TView& c2, int64_t M
     check(hkb_moe_gemm_fp8_blockscale(X.ptr, W.ptr, Y.ptr, (const float*)Xs.ptr, (const float*)Ws.ptr, bias.none ? nullptr : (const float*)bias.ptr,
                                       gather.none ? nullptr : (const int32_t*)gather.ptr, (const int32_t*)hist.ptr, (const int32_t*)offs.ptr,
                                       (const int32_t*)data.ptr, tokens, rows, E, N, K, grid_m, n_expts_act, L.stream));
+}
+
+// moe_op_mxfp4_tk.moe_mxfp4(...): kernels/moe-gemm/moe_op_mxfp4/kernel.cpp:262-349 -- same name, argument names and
+// order.  Strides are checked, not used: A, C and A_mx_scale row-major; B and B_mx_scale K-contiguous per output
+// column (the [E, K/2, N] / [E, K/32, N] views of [E, N, K/2] / [E, N, K/32] storage).
+[[maybe_unused]] void moe_mxfp4(py::object A_, py::object B_, py::object C_, py::object Amx_, py::object Bmx_, py::object As_, py::object Bs_,
+                                py::object tw_, py::object ids_, py::object eids_, int64_t N, int64_t K, int64_t num_valid_tokens,
+                                int64_t top_k, bool mul_routed_weight, int64_t stride_am, int64_t stride_ak, int64_t stride_be,
+                                int64_t stride_bk, int64_t stride_bn, int64_t stride_cm, int64_t stride_cn, int64_t stride_amxm,
+                                int64_t stride_amxk, int64_t stride_bmxe, int64_t stride_bmxk, int64_t stride_bmxn, int64_t grid_m,
+                                int64_t grid_n) {
+    (void)grid_n;
+    TView A = view(A_, "A"), B = view(B_, "B", false, false), C = view(C_, "C"), Amx = view(Amx_, "A_mx_scale"),
+          Bmx = view(Bmx_, "B_mx_scale", false, false), As = view(As_, "A_scale", true), Bs = view(Bs_, "B_scale", true),
+          tw = view(tw_, "topk_weights", true), ids = view(ids_, "sorted_token_ids"), eids = view(eids_, "expert_ids");
+    want_dtype(A, "A", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(B, "B", {"uint8", "float4_e2m1fn_x2"});
+    want_dtype(C, "C", {"bfloat16"});
+    want_dtype(Amx, "A_mx_scale", {"uint8", "float8_e8m0fnu"});
+    want_dtype(Bmx, "B_mx_scale", {"uint8", "float8_e8m0fnu"});
+    for (const TView* t : {&As, &Bs, &tw})
+        if (!t->none) want_dtype(*t, t->name, {"float32"});
+    want_dtype(ids, "sorted_token_ids", {"int32"});
+    want_dtype(eids, "expert_ids", {"int32"});
+    if (K % 128 || A.rank() != 2 || A.dim(1) != K / 2 || C.rank() != 2 || C.dim(1) != N) fail("A must be [tokens, K/2] and C [rows, N], K a multiple of 128");
+    const int64_t tokens = A.dim(0), num_padded = ids.numel;
+    if (B.numel % (N * (K / 2))) fail("B must hold E*N*K/2 bytes");
+    const int64_t E = B.numel / (N * (K / 2));
+    if (eids.numel * 128 != num_padded || grid_m != eids.numel) fail("sorted_token_ids must hold 128 entries per entry of expert_ids (grid_m blocks)");
+    if (C.dim(0) < num_valid_tokens) fail("C must have a row per valid (token, k) index");
+    if (stride_ak != 1 || stride_am != K / 2 || stride_cn != 1 || stride_cm != N) fail("A and C must be row-major and contiguous");
+    if (stride_bk != 1 || stride_bn != K / 2 || stride_be != N * (K / 2))
+        fail("B must be K-contiguous per output column: store the weights as [E, N, K/2] and pass the [E, K/2, N] view "
+             "(stride_be = N*K/2, stride_bk = 1, stride_bn = K/2)");
+    if (Amx.numel != tokens * (K / 32) || stride_amxk != 1 || stride_amxm != K / 32) fail("A_mx_scale must be contiguous [tokens, K/32]");
+    if (Bmx.numel != E * N * (K / 32) || stride_bmxk != 1 || stride_bmxn != K / 32 || stride_bmxe != N * (K / 32))
+        fail("B_mx_scale must be K-contiguous per output column: [E, N, K/32] storage passed as the [E, K/32, N] view");
+    if (!Bs.none && Bs.numel != E) fail("B_scale must have one entry per expert");
+    if (mul_routed_weight && (tw.none || tw.numel < num_valid_tokens)) fail("topk_weights must have an entry per valid (token, k) index");
+    same_device({&A, &B, &C, &Amx, &Bmx, &As, &Bs, &tw, &ids, &eids});
+    Launch L(A.device);
+    check(hkb_moe_gemm_mxfp4(A.ptr, B.ptr, C.ptr, Amx.ptr, Bmx.ptr, As.none ? nullptr : (const float*)As.ptr, Bs.none ? nullptr : (const float*)Bs.ptr,
+                             tw.none ? nullptr : (const float*)tw.ptr, (const int32_t*)ids.ptr, (const int32_t*)eids.ptr, tokens, num_padded, E,
+                             N, K, num_valid_tokens, top_k, mul_routed_weight ? 1 : 0, L.stream));
 }
 
 // quant_moe_tk: kernels/moe-misc/quant_moe/kernel.cpp:392-476 (same names, argument order and the
@@ -644,6 +677,12 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
           "ExptHist"_a, "ExptOffs"_a, "ExptData"_a, "N"_a, "K"_a, "group_k"_a, "group_n"_a, "grid_m"_a, "grid_n"_a, "n_expts_act"_a,
           "stride_ym"_a, "stride_yn"_a, "stride_xm"_a, "stride_xk"_a, "stride_we"_a, "stride_wk"_a, "stride_wn"_a,
           "stride_xsm"_a, "stride_xsk"_a, "stride_wse"_a, "stride_wsk"_a, "stride_wsn"_a);
+#elif defined(HKB_SHIM_MOE_OP_MXFP4)
+    m.doc() = "MoE grouped MXFP4 x MXFP4 GEMM over a padded, expert-sorted row list, sm_100a tcgen05 block-scaled MMA";
+    m.def("moe_mxfp4", &moe_mxfp4, "A"_a, "B"_a, "C"_a, "A_mx_scale"_a, "B_mx_scale"_a, "A_scale"_a, "B_scale"_a, "topk_weights"_a,
+          "sorted_token_ids"_a, "expert_ids"_a, "N"_a, "K"_a, "num_valid_tokens"_a, "top_k"_a, "mul_routed_weight"_a, "stride_am"_a,
+          "stride_ak"_a, "stride_be"_a, "stride_bk"_a, "stride_bn"_a, "stride_cm"_a, "stride_cn"_a, "stride_amxm"_a, "stride_amxk"_a,
+          "stride_bmxe"_a, "stride_bmxk"_a, "stride_bmxn"_a, "grid_m"_a, "grid_n"_a);
 #elif defined(HKB_SHIM_QUANT_MOE)
     m.doc() = "MoE casts: static FP8 down-cast, MX (e4m3 / e2m1 + exponent byte per 32) down- and up-cast, sm_100a";
     m.def("downcast_to_static_fp8", &downcast_to_static_fp8, "x"_a, "y"_a, "scale"_a, "M"_a, "N"_a);

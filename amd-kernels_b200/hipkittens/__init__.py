@@ -201,6 +201,7 @@ class _FusedGemmNamespace:
 class _MoeGemmNamespace:
     # grouped (per-expert) quantized GEMMs over expert-sorted rows
     a8w8_blockscale = _SubModule("moe_op_gemm_a8w8_blockscale_tk")
+    mxfp4 = _SubModule("moe_op_mxfp4_tk")
     # names kept for compatibility; not built here (bf16 / int4 / fused-activation variants)
     gemm = _SubModule("moe_op_tk")
     e2e = _SubModule("moe_op_e2e_tk")
@@ -209,7 +210,6 @@ class _MoeGemmNamespace:
     a4w4 = _SubModule("moe_op_gemm_a4w4_tk")
     a8w4 = _SubModule("moe_op_gemm_a8w4_tk")
     a8w8 = _SubModule("moe_op_gemm_a8w8_tk")
-    mxfp4 = _SubModule("moe_op_mxfp4_tk")
     mxfp4_silu_fused = _SubModule("moe_op_mxfp4_silu_fused_tk")
 
 

@@ -242,6 +242,25 @@ int hkb_moe_gemm_fp8_blockscale(const void* X, const void* W, void* Y, const flo
                                 int64_t rows, int64_t E, int64_t N, int64_t K, int64_t grid_m,
                                 int64_t n_expts_act, void* stream);
 
+/* Grouped (MoE) MXFP4 GEMM over a padded, expert-sorted row list: block mb (128 rows) of the list belongs to
+ * expert expert_ids[mb] (-1: no expert, zeros are written); sorted row r names the flat (token, k) index
+ * id = sorted_token_ids[r] (id >= num_valid_tokens: padding, skipped), reads activation row id / top_k and
+ * writes output row id:
+ *   C[id, n] = bf16( dq(A[id/top_k]) . dq(B[e, n]) * A_scale[0] * B_scale[e] * (mul_routed_weight ? topk_weights[id] : 1) )
+ * A u8 [tokens, K/2] + A_mx_scale u8 [tokens, K/32]; B u8 [E, N, K/2] + B_mx_scale u8 [E, N, K/32] (K-contiguous);
+ * C bf16 [num_valid_tokens, N]; A_scale (1 float), B_scale ([E]) and topk_weights may be NULL.  num_padded (the
+ * length of sorted_token_ids) is a multiple of 128; K % 128 == 0, N % 8 == 0.  Rows and scales are first brought
+ * into expert-sorted order / the tensor core's layout in per-(device, stream) scratch.  Replaces
+ * moe_mxfp4(A, B, C, A_mx_scale, B_mx_scale, A_scale, B_scale, topk_weights, sorted_token_ids, expert_ids, N, K,
+ * num_valid_tokens, top_k, mul_routed_weight, strides..., grid_m, grid_n):
+ *   kernels/moe-gemm/moe_op_mxfp4/kernel.cpp:38-66,90-238,262-349. */
+int hkb_moe_gemm_mxfp4(const void* A, const void* B, void* C, const void* A_mx_scale,
+                       const void* B_mx_scale, const float* A_scale_or_null,
+                       const float* B_scale_or_null, const float* topk_weights_or_null,
+                       const int32_t* sorted_token_ids, const int32_t* expert_ids, int64_t tokens,
+                       int64_t num_padded, int64_t E, int64_t N, int64_t K,
+                       int64_t num_valid_tokens, int64_t top_k, int mul_routed_weight, void* stream);
+
 /* quant_moe_tk: wire formats of the MoE activation/weight casts.  Replace
  *   quant_moe_tk.downcast_to_static_fp8(x, y, scale, M, N)
  *   quant_moe_tk.downcast_to_mxfp(mx_tensor, mx_scale, src, outer_dim, quant_dim, is_fp4)

@@ -183,6 +183,40 @@ def moe_gemm_blockscale(X, W, x_scale, w_scale, gather, hist, offs, expt_data, n
     return Y
 
 
+def moe_gemm_mxfp4(A, B, A_mx, B_mx, a_scale, b_scale, sorted_ids, expert_ids, topk_weights, num_valid, top_k,
+                   mul_weight=True, index="token", block_m=128):
+    """Grouped (MoE) MXFP4 GEMM over a padded, expert-sorted row list.  A u8 [tokens, K/2] + A_mx u8 [tokens, K/32];
+    B u8 [E, N, K/2] + B_mx u8 [E, N, K/32].  For block b with expert e = expert_ids[b] != -1 and sorted row
+    t = b*block_m + lm with id = sorted_ids[t] < num_valid:
+        result = dq(A[id // top_k]) . dq(B[e])^T * a_scale * b_scale[e]   (* weight when mul_weight)
+    index="token"  -- the reference device code (kernels/moe-gemm/moe_op_mxfp4/kernel.cpp:118-131,215-238): output row
+                      and weight index are `id`;
+    index="sorted" -- the reference's Python restatement (test_parity.py:79-115): both are the sorted position t.
+    Returns fp32 [num_valid or num_padded, N]."""
+    Adq = dequant_mxfp4(A, A_mx)
+    E = np.asarray(B).shape[0]
+    Bdq = [dequant_mxfp4(np.asarray(B)[e], np.asarray(B_mx)[e]) for e in range(E)]
+    N = Bdq[0].shape[0]
+    sorted_ids = np.asarray(sorted_ids)
+    rows = num_valid if index == "token" else len(sorted_ids)
+    C = np.zeros((rows, N), dtype=np.float32)
+    for b, e in enumerate(np.asarray(expert_ids).tolist()):
+        if e < 0:
+            continue
+        t = np.arange(b * block_m, min((b + 1) * block_m, len(sorted_ids)))
+        ids = sorted_ids[t]
+        ok = ids < num_valid
+        t, ids = t[ok], ids[ok]
+        if len(ids) == 0:
+            continue
+        res = (_t(Adq[ids // top_k]) @ _t(Bdq[e]).T).numpy() * np.float32(np.float32(a_scale) * np.float32(np.asarray(b_scale)[e]))
+        out = ids if index == "token" else t
+        if mul_weight:
+            res = res * _f32(topk_weights)[out][:, None]
+        C[out] = res
+    return C
+
+
 def split_cat(G, y, S1, S2):
     """Split-concatenate epilogue of the *_split_cat GEMMs on a GEMM result G [M, D*(S1+S2)] and
     y [M, D, S3] (kernels/gemm-fused/fused_gemm_a8w8_blockscale_split_cat/test_parity.py:45-56):

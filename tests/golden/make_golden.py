@@ -24,6 +24,8 @@ Fixtures (all seed 42, the reference tests' seed):
       (its D, S1, S2, S3), inputs and outputs
   moe_gemm_blockscale.npz    generate_ogs_routing + reference_moe_a8w8_bs of
       kernels/moe-gemm/moe_op_gemm_a8w8_blockscale/test_parity.py:29-99 (96 tokens, 4 experts, top-2, K=N=256, group 128)
+  moe_gemm_mxfp4.npz         generate_routing + reference_moe_mxfp4 of kernels/moe-gemm/moe_op_mxfp4/test_parity.py:49-115
+      (80 tokens, 3 experts, top-2, K=128, N=64; output and weights indexed by sorted position, as that script does)
   gemm_ptgq.npz              reference_torch of kernels/gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py:40-82
       (B=4, 128^3, bias; A bf16, int8 weights, scalar weight scale, output bf16)
   e2m1_lut.npz               FP4_LUT / decode_mx_scale of kernels/moe-gemm/moe_op_mxfp4/test_parity.py:30-46
@@ -128,6 +130,21 @@ def main():
     Y = mo.reference_moe_a8w8_bs(X, Wm, xs, wsc, gather, hist, offs, expt_data, top_k, 128, 128)
     np.savez_compressed(os.path.join(HERE, "moe_gemm_blockscale.npz"), X=X, W_nk=Wm.transpose(0, 2, 1).copy(), x_scale=xs,
                         w_scale=wsc, hist=hist, offs=offs, gather=gather, expt_data=expt_data, top_k=top_k, Y=Y)
+
+    mx = _load(os.path.join(k, "moe-gemm/moe_op_mxfp4/test_parity.py"), "ref_moe_mxfp4")
+    np.random.seed(42)
+    tokens, E, top_k, Kd, Nd = 80, 3, 2, 128, 64
+    A = np.random.randint(0, 255, (tokens, Kd // 2)).astype(np.uint8)
+    Bm = np.random.randint(0, 255, (E, Kd // 2, Nd)).astype(np.uint8)          # the reference's [E, K/2, N] form
+    A_mx = np.random.randint(120, 134, (tokens, Kd // 32)).astype(np.uint8)
+    B_mx = np.random.randint(120, 134, (E, Kd // 32, Nd)).astype(np.uint8)
+    a_scale = np.float32(0.01)
+    b_scale = (np.random.rand(E).astype(np.float32) * 0.01)
+    ids, block_experts, weights, num_padded, num_valid = mx.generate_routing(tokens, E, top_k)
+    Cm = mx.reference_moe_mxfp4(A, Bm, A_mx, B_mx, a_scale, b_scale, ids, block_experts, weights, num_valid, top_k, Kd, mul_weight=True)
+    np.savez_compressed(os.path.join(HERE, "moe_gemm_mxfp4.npz"), A=A, B_nk=Bm.transpose(0, 2, 1).copy(), A_mx=A_mx,
+                        B_mx_nk=B_mx.transpose(0, 2, 1).copy(), a_scale=a_scale, b_scale=b_scale, sorted_ids=ids,
+                        expert_ids=block_experts, weights_sorted=weights, num_valid=num_valid, top_k=top_k, C_sorted=Cm)
 
     pq = _load(os.path.join(k, "gemm-batched/batched_gemm_a8w8_ptgq/test_parity.py"), "ref_ptgq")
     A, B_int8, b_scale, bias, C = pq.reference_torch()          # A [B,M,K] bf16, B [B,K,N] int8, bias [B,1,N] bf16

@@ -132,7 +132,7 @@ HOT_MODULES = ["quant_tk", "fused_fp8_quant_tk", "fused_mxfp4_quant_tk", "gemm_a
                "gemm_a8w8_blockscale_tk", "gemm_afp4wfp4_tk", "batched_gemm_a8w8_tk", "batched_gemm_afp4wfp4_tk",
                "fused_gemm_a8w8_blockscale_mul_add_tk", "fused_gemm_afp4wfp4_mul_add_tk", "quant_moe_tk",
                "batched_gemm_a8w8_ptgq_tk", "fused_gemm_a8w8_blockscale_split_cat_tk", "fused_gemm_afp4wfp4_split_cat_tk",
-               "moe_op_gemm_a8w8_blockscale_tk"]
+               "moe_op_gemm_a8w8_blockscale_tk", "moe_op_mxfp4_tk"]
 
 
 def test_loader_discovers_the_reference_module_names(hk):

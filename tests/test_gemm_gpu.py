@@ -450,6 +450,71 @@ def test_moe_gemm_blockscale_without_gather_and_layout_check(hk):
                                                         N, K, 128, 128, 3, 6, 1, N, 1, K, 1, K * N, N, 1, 2, 1, 6, 3, 1)
 
 
+def _moe_mxfp4_routing(tokens, E, top_k, seed, block_m=128):
+    """Padded expert-sorted row list with every expert's rows padded to whole blocks (the form fused-MoE
+    routing produces): sorted_ids (padding = tokens*top_k), expert per block, routing weight per flat index."""
+    rng = np.random.RandomState(seed)
+    assigns = rng.randint(0, E, (tokens, top_k))
+    total = tokens * top_k
+    ids, experts = [], []
+    for e in range(E):
+        mine = np.nonzero(assigns.ravel() == e)[0].astype(np.int32)
+        pad = (-len(mine)) % block_m
+        ids.append(np.concatenate([mine, np.full(pad, total, dtype=np.int32)]))
+        experts += [e] * ((len(mine) + pad) // block_m)
+    ids.append(np.full(block_m, total, dtype=np.int32))          # one block without an expert
+    experts.append(-1)
+    w = rng.rand(total).astype(np.float32)
+    return np.concatenate(ids), np.array(experts, dtype=np.int32), w, total
+
+
+def _moe_mxfp4_call(hk, A, B_nk, C, A_mx, B_mx_nk, a_scale, b_scale, w, ids, eids, num_valid, top_k, mul):
+    E, N, K2 = B_nk.shape
+    K = K2 * 2
+    hk.moe_gemm.mxfp4.moe_mxfp4(A, B_nk.transpose(1, 2), C, A_mx, B_mx_nk.transpose(1, 2), a_scale, b_scale, w, ids, eids, N, K,
+                                num_valid, top_k, mul, K // 2, 1, N * K // 2, 1, K // 2, N, 1, K // 32, 1, N * K // 32, 1, K // 32,
+                                eids.numel(), (N + 127) // 128)
+
+
+@pytest.mark.parametrize("tokens,E,top_k,K,N,mul", [(80, 3, 2, 128, 64, True), (600, 8, 2, 512, 1024, True), (5000, 8, 4, 1024, 3072, False)])
+def test_moe_gemm_mxfp4(hk, tokens, E, top_k, K, N, mul):
+    g = torch.Generator().manual_seed(91)
+    ac, asc = quant.quant_mxfp4(torch.randn(tokens, K, generator=g).bfloat16())
+    wc = np.empty((E, N, K // 2), dtype=np.uint8); wsc = np.empty((E, N, K // 32), dtype=np.uint8)
+    for e in range(E):
+        wc[e], wsc[e] = quant.quant_mxfp4((torch.randn(N, K, generator=g) * 0.02).bfloat16())
+    ids, eids, w, total = _moe_mxfp4_routing(tokens, E, top_k, seed=6)
+    a_scale = np.float32(0.5)
+    b_scale = (np.random.RandomState(1).rand(E).astype(np.float32) + 0.5)
+    C = torch.full((total, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _moe_mxfp4_call(hk, _dev(ac), _dev(wc), C, _dev(asc), _dev(wsc), torch.full((1,), float(a_scale), device=DEV), _dev(b_scale), _dev(w),
+                    _dev(ids), _dev(eids), total, top_k, mul)
+    assert "grouped" in hk.last_kernel()
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = gemm.moe_gemm_mxfp4(ac, wc, asc, wsc, a_scale, b_scale, ids, eids, w, total, top_k, mul_weight=mul, index="token")
+    assert not torch.isnan(C.float()).any()               # every (token, k) row is named by the list
+    _check(C, ref, f"moe mxfp4 tokens={tokens} E={E}")
+
+
+def test_moe_gemm_mxfp4_reference_golden(hk, golden_dir):
+    """The reference's own routing generator (blocks take the expert of their first row) and data; its Python
+    restatement indexes output rows and weights by sorted position, its device code by flat (token, k) index:
+    the kernel follows the device code, the same numbers land in other rows."""
+    g = np.load(os.path.join(golden_dir, "moe_gemm_mxfp4.npz"))
+    nv, tk = int(g["num_valid"]), int(g["top_k"])
+    valid = g["sorted_ids"] < nv
+    w_by_id = np.zeros(nv, dtype=np.float32)
+    w_by_id[g["sorted_ids"][valid]] = g["weights_sorted"][valid]
+    N = g["B_nk"].shape[1]
+    C = torch.zeros(nv, N, dtype=torch.bfloat16, device=DEV)
+    _moe_mxfp4_call(hk, _dev(g["A"]), _dev(g["B_nk"]), C, _dev(g["A_mx"]), _dev(g["B_mx_nk"]), torch.full((1,), float(g["a_scale"]), device=DEV),
+                    _dev(g["b_scale"]), _dev(w_by_id), _dev(g["sorted_ids"]), _dev(g["expert_ids"]), nv, tk, True)
+    torch.cuda.synchronize()
+    _status_ok()
+    _check(C[torch.from_numpy(g["sorted_ids"][valid]).long().to(DEV)], g["C_sorted"][valid], "moe mxfp4 golden")
+
+
 # ---- bounded waits -----------------------------------------------------------------------------
 
 def test_bounded_wait_gives_up_by_itself_and_the_device_stays_usable(hk):

@@ -203,6 +203,22 @@ def test_moe_gemm_blockscale_golden(golden_dir):
     assert (np.abs(g["Y"]).sum(axis=1) > 0).all()        # every sorted row belongs to a tile
 
 
+def test_moe_gemm_mxfp4_golden(golden_dir):
+    """The oracle in the indexing of the reference's Python restatement (output row and routing weight by sorted
+    position) reproduces reference_moe_mxfp4(); in the reference device code's indexing (by flat (token, k) index)
+    it is the same numbers in different rows."""
+    g = np.load(os.path.join(golden_dir, "moe_gemm_mxfp4.npz"))
+    args = (g["A"], g["B_nk"], g["A_mx"], g["B_mx_nk"], g["a_scale"], g["b_scale"], g["sorted_ids"], g["expert_ids"])
+    nv, tk = int(g["num_valid"]), int(g["top_k"])
+    C = gemm.moe_gemm_mxfp4(*args, g["weights_sorted"], nv, tk, index="sorted")
+    np.testing.assert_allclose(C, g["C_sorted"], rtol=2e-5, atol=1e-7)
+    w_by_id = np.zeros(nv, dtype=np.float32)
+    valid = g["sorted_ids"] < nv
+    w_by_id[g["sorted_ids"][valid]] = g["weights_sorted"][valid]
+    Ct = gemm.moe_gemm_mxfp4(*args, w_by_id, nv, tk, index="token")
+    np.testing.assert_allclose(Ct[g["sorted_ids"][valid]], g["C_sorted"][valid], rtol=2e-5, atol=1e-7)
+
+
 def test_split_cat_golden(golden_dir):
     """Block-scale GEMM + split-cat oracle against the reference's reference_blockscale_gemm_split_cat()."""
     g = np.load(os.path.join(golden_dir, "fused_blockscale_split_cat.npz"))
