@@ -98,33 +98,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// A counter in shared memory as a cheaper hand-off than an mbarrier where one thread waits for a known
-// number of arrivals: arrivals add 1 with release semantics, the waiter polls with acquire loads until the
-// counter has reached `target` (wrap-around safe).  Bounded like mbar_wait.
-__device__ __forceinline__ void counter_add_release(uint32_t addr) {
-    asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(addr) : "memory");
-}
-__device__ __forceinline__ bool counter_wait(uint32_t addr, uint32_t target, volatile uint32_t* abort_flag,
-                                             uint32_t* status, uint32_t err_bit, uint64_t limit_ns = kWaitLimitNs) {
-    uint64_t t0 = 0;
-    uint32_t spins = 0;
-    while (true) {
-        uint32_t v;
-        asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-        if ((int32_t)(v - target) >= 0) return true;
-        if ((++spins & 0x3FF) == 0) {
-            if (*abort_flag) return false;
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > limit_ns) {
-                *abort_flag = 1;
-                atomicOr(status, err_bit);
-                return false;
-            }
-        }
-    }
-}
-
 // TMA: 3-D tiled load (x = byte offset in the row, y = row, z = batch) into swizzled smem.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int32_t x, int32_t y, int32_t z) {
