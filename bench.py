@@ -13,6 +13,7 @@ synthetic tensors, there is no dataset behind this metric):
        ranks: the default at every --gpus (the largest configuration that fits one GPU), so the
        1/2/4/8-GPU numbers are a strong-scaling curve of one problem
   c2   block-scale FP8, M=4096 N=14336 K=4096
+  c5s  block-scale FP8, M=4096 N=14336 K=8192 (config 5 divided by 4 in M and N: small enough for an ncu capture)
   c3   MXFP4, M=N=K=8192
   c4a  per-token FP8, M=16 N=28672 K=8192 (decode shape, HBM-bound)
   c4b  batched per-token FP8, B=8 M=512 N=4096 K=4096
@@ -57,6 +58,7 @@ WORKLOADS = {
     "c4a": ("pts", 1, 16, 28672, 8192),
     "c4b": ("pts", 8, 512, 4096, 4096),
     "c5": ("blockscale", 1, 16384, 57344, 8192),
+    "c5s": ("blockscale", 1, 4096, 14336, 8192),     # config 5 with M and N divided by 4: the size its kernel is profiled at
     "p8k": ("pts", 1, 8192, 8192, 8192),
     "p2": ("pts", 1, 4096, 14336, 4096),
     "ptgq": ("ptgq", 1, 4096, 14336, 4096),
