@@ -85,6 +85,9 @@ L2_FLUSH_BYTES = 256 << 20
 # Config 5's launch is too large to capture under the profiler (seconds per replayed pass); its
 # figure is config 2's capture scaled by the units processed, see traffic_note in the output.
 NCU_TRAFFIC = {
+    "c5": 5.93e9,        # 16 x the capture of c5s (same kernel, same K, 1/16 of the tiles)
+    "c5s": 370.5e6,
+    "ptgq": 307.7e6,
     "c2": 290.1e6,
     "c3": 204.2e6,
     "c4a": 241.4e6,
@@ -778,7 +781,10 @@ def main():
         peak = (peaks["bf16_sustained"] if sustained else peaks["bf16"]) * mult
         achieved = flops_of(wl.kind, wl.batch, wl.M, wl.N, wl.K) / 1e12 / (dom_ms / 1e3)
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC.get(name), "kernel_ms": dom_ms,
+                "traffic": (NCU_TRAFFIC[name] / world if name in NCU_TRAFFIC else None), "kernel_ms": dom_ms,
+                "traffic_note": ("dram__bytes_read.sum + dram__bytes_write.sum of one ncu-captured launch" +
+                                 (f" of the same kernel on M/4 x N/4 x K, scaled by the units one rank's launch processes (x{16 // world})"
+                                  if name == "c5" else "")) if name in NCU_TRAFFIC else None,
                 "peak_source": f"{mult:g} x dense bf16 cuBLAS {'sustained' if sustained else 'burst'} ({peaks['source']}); "
                                f"fp8 = 2x, fp4 = 4x the bf16 rate per the datasheet ratios"
                                + ("; sustained because one launch lasts milliseconds and runs at the power-limited clock" if sustained else ""),
