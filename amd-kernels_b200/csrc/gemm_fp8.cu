@@ -357,16 +357,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     tc_fence_after();
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (kBlockScale) {
-                        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
-                        tc_fence_after();
-                    }
+                    // The operands usually landed long ago; the accumulator buffer coming back from the epilogue is
+                    // what this thread really waits for.  So: operands first, descriptors ready, then the buffer, and
+                    // the MMAs go out right behind it.
                     if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
-                    tc_fence_after();
                     const uint32_t sa = smem_base + s * L::kStageBytes;
                     const uint64_t da = smem_desc_sw128(sa);
                     const uint64_t db = smem_desc_sw128(sa + L::kABytes);
                     const uint32_t d_tmem = tmem_base + acc * BN;
+                    if (kBlockScale) {
+                        if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
+                    }
+                    tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint32_t accumulate = kBlockScale ? (k != 0) : ((kb | k) != 0);
@@ -374,13 +376,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         if constexpr (kPair) mma_f8_pair(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), IDESC, accumulate);
                         else mma_f8(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), IDESC, accumulate);
                     }
-                    // smem stage free once these MMAs retire (pair mode: in both CTAs)
-                    if constexpr (kPair) tc_commit_pair(empty_bar(s), 3); else tc_commit(empty_bar(s));
                     if (kBlockScale) {
-                        // partial product ready for promotion
+                        // partial product ready for promotion (the epilogue waits for this one: it goes first)
                         if constexpr (kPair) tc_commit_pair(tfull_bar(acc), 3); else tc_commit(tfull_bar(acc));
                         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                     }
+                    // smem stage free once these MMAs retire (pair mode: in both CTAs)
+                    if constexpr (kPair) tc_commit_pair(empty_bar(s), 3); else tc_commit(empty_bar(s));
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!kBlockScale && ok) {
