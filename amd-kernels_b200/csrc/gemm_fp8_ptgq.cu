@@ -41,6 +41,11 @@ constexpr int ASLOTS = 4;            // ring of bf16 activation groups (16 KB ea
 constexpr int GROUP_M = 8;
 constexpr int RING = 16;             // scale ring, in groups: the converter runs at most 2*STAGES + 2 groups ahead of the epilogue
 constexpr int THREADS = 512;
+// Registers per thread after setmaxnreg: first warpgroup (producers, MMA issuer), converter warpgroup, the two
+// epilogue warpgroups.  The sum must stay within the CTA's allocation at launch (512 x 128): an increase beyond it
+// never returns.
+constexpr int kRegsWg0 = 40, kRegsConv = 104, kRegsEpi = 184;
+static_assert(128 * (kRegsWg0 + kRegsConv + 2 * kRegsEpi) <= THREADS * 128, "setmaxnreg budget exceeds the CTA's registers");
 
 struct PtgqParams {
     int M, N, K, batch;
@@ -128,7 +133,7 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        reg_dealloc<40>();
+        reg_dealloc<kRegsWg0>();
         if (warp == 0) {
             // ================= TMA producer (weights) =================
             if (elect_one()) {
@@ -203,7 +208,7 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
     } else if (warp < 8) {
         // ================= converter: bf16 rows -> e4m3 operand tile + scales =================
-        reg_dealloc<104>();
+        reg_dealloc<kRegsConv>();
         const int r = (warp - 4) * 32 + lane;           // row of the tile
         const uint32_t sw = (uint32_t)(r & 7);          // 128-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ (r & 7)
         const float kInv448 = 1.0f / 448.0f;
@@ -254,7 +259,7 @@ gemm_fp8_ptgq_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
     } else {
         // ================= epilogue =================
-        reg_alloc<184>();
+        reg_alloc<kRegsEpi>();
         const int ew = warp - 8;
         const int quarter = warp & 3;
         const int grp = ew >> 2;
