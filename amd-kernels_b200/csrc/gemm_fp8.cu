@@ -130,8 +130,8 @@ struct SmemLayout {
     static constexpr int kBBytes = kBRows * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOffset = STAGES * kStageBytes;
-    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then tmem base + abort flag
-    static constexpr int kNumBars = 2 * STAGES + 4;
+    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], relay[2] (CTA pairs with block scales), then tmem base + abort flag
+    static constexpr int kNumBars = 2 * STAGES + 6;
     static constexpr int kScaleOffset = kBarOffset + ((kNumBars * 8 + 16 + 15) / 16) * 16;
     static constexpr int kSaBytes = 2 * (kScaleChunk / 4) * SCALE_THREADS * 16;     // [2][chunk/4][thread] float4
     static constexpr int kSbBytes = 2 * (SCALE_THREADS / 32) * kScaleChunk * 4;     // [2][warp][chunk] float
@@ -253,6 +253,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto relay_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 4 + a); };
+    // CTA pairs with block scales: the eight epilogue warps of a CTA release a TMEM buffer on a local barrier and
+    // warp 2 forwards ONE arrive per CTA to the leader's barrier, instead of sixteen arrives crossing the cluster
+    constexpr bool kRelay = kPair && kBlockScale;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -275,7 +279,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kPair ? 2 * EPI_WARPS : EPI_WARPS);   // the leader hears both CTAs' epilogues
+            mbar_init(tempty_bar(a), kRelay ? 2 : kPair ? 2 * EPI_WARPS : EPI_WARPS);   // the leader hears both CTAs' epilogues
+            mbar_init(relay_bar(a), EPI_WARPS);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -391,10 +396,24 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
             }
         }
+    } else if (kRelay && warp == 2) {
+        // ================= release relay (CTA pairs with block scales) =================
+        if (elect_one()) {
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            bool ok = true;
+            for (int t = tile0; t < total_tiles && ok; t += tile_step) {
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(relay_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue, p.wait_ns)) { ok = false; break; }
+                    mbar_arrive_cluster(tempty_bar(acc), 0);
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+            }
+        }
     }
     } else {
         // ================= epilogue =================
-        if constexpr (kRegSplit) reg_alloc<kRegsEpi>();   // epilogue warpgroups take the registers WG0 gave up   // epilogue warpgroups take the registers WG0 gave up
+        if constexpr (kRegSplit) reg_alloc<kRegsEpi>();   // epilogue warpgroups take the registers WG0 gave up
         const int ew = warp - EPI_WARP0;         // 0 .. EPI_WARPS-1
         const int quarter = warp & 3;            // TMEM lane quarter this warp may read
         const int grp = ew >> 2;                 // column group
@@ -556,7 +575,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) {
-                            if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0);
+                            if constexpr (kRelay) mbar_arrive(relay_bar(acc));
+                            else if constexpr (kPair) mbar_arrive_cluster(tempty_bar(acc), 0);
                             else mbar_arrive(tempty_bar(acc));
                         }
                     };
