@@ -20,6 +20,7 @@ synthetic tensors, there is no dataset behind this metric):
   c1   per-token FP8, M=128 N=1024 K=1024 (latency-bound parity configuration)
   p8k  per-token FP8, M=N=K=8192 (tuning shape, not a benchmark configuration)
   p2   per-token FP8 on config 2's shape (tuning shape: isolates the block-scale promotion cost)
+  moe-fp8 / moe-mxfp4   grouped (MoE) block-scale FP8 / MXFP4 GEMM: 8192 tokens, top-2 of 8 experts (16384 expert-sorted rows)
   ptgq bf16 activations quantized per row and 64-wide K group inside the GEMM, scalar weight scale, on config 2's shape
   qbw-fp8 / qbw-1x128 / qbw-mxfp4 / qbw-mxfp4-16k   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192, 16384x8192)
   peak-fp8 / peak-fp4   tensor-core ceiling probe: back-to-back tcgen05.mma on resident operands, all SMs
@@ -62,6 +63,9 @@ WORKLOADS = {
     "p8k": ("pts", 1, 8192, 8192, 8192),
     "p2": ("pts", 1, 4096, 14336, 4096),
     "ptgq": ("ptgq", 1, 4096, 14336, 4096),
+    # grouped (MoE) GEMMs: 8192 tokens, top-2 of 8 experts -> M = 16384 expert-sorted rows
+    "moe-fp8": ("moe-fp8", 8, 16384, 14336, 4096),
+    "moe-mxfp4": ("moe-mxfp4", 8, 16384, 8192, 8192),
     "qbw-fp8": ("quant-fp8", 1, 16384, 0, 8192),
     "qbw-1x128": ("quant-1x128", 1, 16384, 0, 8192),
     "qbw-mxfp4": ("quant-mxfp4", 1, 8192, 0, 8192),
@@ -167,6 +171,8 @@ class ClockSampler:
 
 
 def flops_of(kind, batch, M, N, K):
+    if kind.startswith("moe"):          # batch = experts; every one of the M sorted rows meets one expert's [N, K]
+        return 2.0 * M * N * K
     return 2.0 * batch * M * N * K
 
 
@@ -225,6 +231,9 @@ class Workload:
         # N-sharding: this rank owns columns [n0, n1)
         n0, n1 = sharded.shard_bounds(N, world, rank) if world > 1 else (0, N)
         self.N_total, self.N = N, n1 - n0
+        if self.kind.startswith("moe"):
+            self._init_moe(hk, g, dev, rank)
+            return
         ashape = (M, K) if B == 1 else (B, M, K)
         wshape = (self.N, K) if B == 1 else (B, self.N, K)
         A = torch.randn(ashape, generator=g, device=dev, dtype=torch.float32).bfloat16()
@@ -276,11 +285,63 @@ class Workload:
         self.launches_per_step = 1 if self.kind == "ptgq" else 2        # quantizer + GEMM (one fused kernel for ptgq)
         torch.cuda.synchronize()
 
+    def _init_moe(self, hk, g, dev, rank):
+        """Routing tables of 8192 tokens with top-2 of E experts (uniform), rows sorted by expert and padded to
+        128-row blocks per expert; per-expert weights ~ N(0, 0.02) quantized once."""
+        import numpy as np
+        E, rows, N, K = self.batch, self.M, self.N, self.K
+        top_k = 2
+        tokens = rows // top_k
+        self.tokens, self.top_k = tokens, top_k
+        rng = np.random.RandomState(42)
+        assigns = rng.randint(0, E, (tokens, top_k))
+        flat = assigns.ravel()
+        order = np.argsort(flat, kind="stable").astype(np.int32)
+        hist = np.bincount(flat, minlength=E).astype(np.int32)
+        self.A = torch.randn(tokens, K, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        gw = torch.Generator(device=dev).manual_seed(1000 + rank)
+        self.C = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+        if self.kind == "moe-fp8":
+            offs = np.concatenate([[0], np.cumsum(hist)[:-1]]).astype(np.int32)
+            tiles = [e | (b << 16) for e in range(E) for b in range((hist[e] + 127) // 128)]
+            self.gather = torch.from_numpy(order).to(dev)
+            self.hist, self.offs = torch.from_numpy(hist).to(dev), torch.from_numpy(offs).to(dev)
+            self.data = torch.tensor(tiles, dtype=torch.int32, device=dev)
+            self.Wq = torch.empty(E, N, K, dtype=torch.uint8, device=dev)
+            self.sw = torch.empty(E, K // 128, N // 128, dtype=torch.float32, device=dev)
+            for e in range(E):
+                w = (torch.randn(N, K, generator=gw, device=dev) * 0.02).bfloat16()
+                hk.weight_quant_128x128(w, self.Wq[e], self.sw[e])
+            self.Aq = torch.empty(tokens, K, dtype=torch.uint8, device=dev)
+            self.sa = torch.empty(tokens, K // 128, dtype=torch.float32, device=dev)
+            self.launches_per_step = 3                                       # quantizer, row gather, grouped GEMM
+        else:
+            ids, experts = [], []
+            for e in range(E):
+                mine = np.nonzero(flat == e)[0].astype(np.int32)
+                pad = (-len(mine)) % 128
+                ids.append(np.concatenate([mine, np.full(pad, rows, dtype=np.int32)]))
+                experts += [e] * ((len(mine) + pad) // 128)
+            self.ids = torch.from_numpy(np.concatenate(ids)).to(dev)
+            self.eids = torch.tensor(experts, dtype=torch.int32, device=dev)
+            self.topk_w = torch.rand(rows, device=dev)
+            self.Wq = torch.empty(E, N, K // 2, dtype=torch.uint8, device=dev)
+            self.sw = torch.empty(E, N, K // 32, dtype=torch.uint8, device=dev)
+            for e in range(E):
+                w = (torch.randn(N, K, generator=gw, device=dev) * 0.02).bfloat16()
+                hk.fused_rmsnorm_mxfp4_quant_fwd(w, None, self.Wq[e], self.sw[e], 1e-6)
+            self.Aq = torch.empty(tokens, K // 2, dtype=torch.uint8, device=dev)
+            self.sa = torch.empty(tokens, K // 32, dtype=torch.uint8, device=dev)
+            self.launches_per_step = 5                                       # quantizer, row gather, 2 scale re-layouts, grouped GEMM
+        torch.cuda.synchronize()
+
     # -- device-resident step ------------------------------------------------------------
     def quantize(self, A):
         hk, K = self.hk, self.K
-        if self.kind == "blockscale":
+        if self.kind in ("blockscale", "moe-fp8"):
             hk.fused_rmsnorm_fp8_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
+        elif self.kind == "moe-mxfp4":
+            hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, self.Aq, self.sa, 1e-6)
         elif self.kind == "ptgq":
             self.A_cur = A                       # quantized inside the GEMM
         elif self.kind == "pts":
@@ -314,6 +375,18 @@ class Workload:
                 hk.gemm.a8w8_per_token.dispatch(self.Aq, self.Wq, C, self.sa, self.sw)
             else:
                 hk.batched_gemm.a8w8.dispatch(self.Aq, self.Wq, self.sa, self.sw, C, None)
+        elif self.kind == "moe-fp8":
+            E, N, K = self.batch, self.N, self.K
+            kb, nb = K // 128, N // 128
+            hk.moe_gemm.a8w8_blockscale.moe_a8w8_blockscale(
+                self.Aq, self.Wq.transpose(1, 2), C, self.sa, self.sw, None, self.gather, self.hist, self.offs, self.data, N, K, 128, 128,
+                self.data.numel(), N // 128, self.top_k, N, 1, K, 1, N * K, 1, K, kb, 1, kb * nb, nb, 1)
+        elif self.kind == "moe-mxfp4":
+            E, N, K = self.batch, self.N, self.K
+            hk.moe_gemm.mxfp4.moe_mxfp4(
+                self.Aq, self.Wq.transpose(1, 2), C, self.sa, self.sw.transpose(1, 2), None, None, self.topk_w, self.ids, self.eids, N, K,
+                self.M, self.top_k, True, K // 2, 1, N * K // 2, 1, K // 2, N, 1, K // 32, 1, N * K // 32, 1, K // 32,
+                self.eids.numel(), N // 128)
         elif self.kind == "ptgq":
             hk.batched_gemm.a8w8_ptgq.dispatch(getattr(self, "A_cur", self.A), self.Wq, self.sw, C, None)
         elif self.kind == "mxfp4":
@@ -438,7 +511,7 @@ class Workload:
         """(units of work per step over ALL ranks, unit name)"""
         if self.kind.startswith("quant"):
             return quant_bytes(self.kind, self.M, self.K) * world / 1e9, "GB/s"
-        n = self.N_total if world > 1 else self.N
+        n = getattr(self, "N_total", self.N) if world > 1 else self.N
         return flops_of(self.kind, self.batch, self.M, n, self.K) / 1e12, "TFLOP/s"
 
 
@@ -584,6 +657,9 @@ def cpu_reference_step(name, sample_rows):
     import numpy as np
     from oracle import gemm as ogemm, quant as oquant, quant_moe as omoe
     kind, B, M, N, K = WORKLOADS[name]
+    if kind.startswith("moe"):
+        # the CPU arm times the same per-row work against one expert's weights (routing adds no arithmetic)
+        kind, B = ("blockscale" if kind == "moe-fp8" else "mxfp4"), 1
     if N > CPU_SAMPLE_MAX_N:
         N = CPU_SAMPLE_MAX_N // 128 * 128
     g = torch.Generator().manual_seed(42)
@@ -652,6 +728,8 @@ cpu_reference_step.cache = {}
 
 def default_sample_rows(name):
     kind, B, M, N, K = WORKLOADS[name]
+    if kind.startswith("moe"):
+        B = 1
     if kind.startswith("quant"):
         return 1024
     # about 0.3 TFLOP of matmul per step: a second or so on a many-core host
@@ -772,7 +850,7 @@ def main():
                 "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC.get(name),
                 "peak_source": f"HBM copy bandwidth, {peaks['source']}", "kernel_ms": dom_ms}
     else:
-        mult = 4.0 if wl.kind == "mxfp4" else 2.0
+        mult = 4.0 if "mxfp4" in wl.kind else 2.0
         # Which cuBLAS figure is the fair denominator: the burst one was taken on launches of well under
         # a millisecond at the full clock, the sustained one with the 1 kW limit setting the clock.  A
         # launch of several milliseconds pulls the limit within itself (the clock samples below show
@@ -935,8 +1013,8 @@ def main():
         kind, B, M, N, K = WORKLOADS[name]
         out = {"metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-               "vs_baseline": None, "dtype": {"mxfp4": "fp4 (e2m1, e8m0 scales), fp32 accumulate"}.get(
-                   kind, "fp8 (e4m3fn), fp32 accumulate"),
+               "vs_baseline": None, "dtype": ("fp4 (e2m1, e8m0 scales), fp32 accumulate" if "mxfp4" in kind
+                                              else "fp8 (e4m3fn), fp32 accumulate"),
                "data": "synthetic", "config": config_of(name, world),
                "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
                "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
