@@ -123,6 +123,19 @@ const char* hkb_last_kernel(void) { return hkb::g_last_kernel; }
 
 const char* hkb_last_error(void) { return hkb::g_err.c_str(); }
 
+int hkb_shard_bounds(int64_t N, int64_t world_size, int64_t rank, int64_t* n0, int64_t* n1) {
+    using namespace hkb;
+    HKB_REQUIRE(n0 && n1, HKB_ERR_BAD_ARG, "shard_bounds: null pointer");
+    HKB_REQUIRE(N > 0 && N % 128 == 0, HKB_ERR_BAD_SHAPE, "shard_bounds: N=%lld must be a positive multiple of 128", (long long)N);
+    HKB_REQUIRE(world_size >= 1 && rank >= 0 && rank < world_size, HKB_ERR_BAD_ARG, "shard_bounds: rank %lld outside a world of %lld",
+                (long long)rank, (long long)world_size);
+    const int64_t blocks = N / 128, base = blocks / world_size, extra = blocks % world_size;
+    const int64_t b0 = rank * base + (rank < extra ? rank : extra);
+    *n0 = b0 * 128;
+    *n1 = (b0 + base + (rank < extra ? 1 : 0)) * 128;
+    return HKB_OK;
+}
+
 int hkb_release(void) {
     using namespace hkb;
     int ndev = 0;

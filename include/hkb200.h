@@ -148,6 +148,12 @@ int hkb_gemm_fp8_blockscale_scatter(const void* A, const void* B, void* const* C
                                     int64_t ldc, const float* sa, const float* sb, int64_t M,
                                     int64_t N, int64_t K, void* stream);
 
+/* The column partition of the N-sharded GEMM: rank `rank` of `world_size` owns output columns (= rows of
+ * B and columns of b_scale / 128) [*n0, *n1): N is cut into 128-wide blocks which are dealt out as evenly
+ * as possible, the first (N/128) % world_size ranks get one more.  Host arithmetic only; the same rule as
+ * hipkittens.sharded.shard_bounds.  No counterpart in the reference project. */
+int hkb_shard_bounds(int64_t N, int64_t world_size, int64_t rank, int64_t* n0, int64_t* n1);
+
 /* The same GEMM with the multiply-add epilogue fused in: C = bf16( c_a * gemm + c_b ), c_a and
  * c_b bf16 [M, N] (16-byte aligned), evaluated in fp32 before the one rounding to bf16.  Replaces
  * fused_gemm_a8w8_blockscale_mul_add_tk.dispatch(a,b,c,a_scale,b_scale,c_a,c_b):

@@ -29,6 +29,20 @@ def test_shard_bounds_cover_n_without_overlap():
         sharded.shard_bounds(1024, 2, 2)
 
 
+def test_c_abi_shard_bounds_agree_with_the_python_rule():
+    import ctypes
+    lib = ctypes.CDLL(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "amd-kernels_b200", "kernels", "libhkb200.so"))
+    i64 = ctypes.c_int64
+    for N, g in [(57344, 8), (57344, 3), (1024, 3), (128, 2), (384, 2)]:
+        for r in range(g):
+            a, b = i64(), i64()
+            assert lib.hkb_shard_bounds(i64(N), i64(g), i64(r), ctypes.byref(a), ctypes.byref(b)) == 0
+            assert (a.value, b.value) == sharded.shard_bounds(N, g, r)
+    a, b = i64(), i64()
+    assert lib.hkb_shard_bounds(i64(1000), i64(2), i64(0), ctypes.byref(a), ctypes.byref(b)) == -2
+    assert lib.hkb_shard_bounds(i64(1024), i64(2), i64(2), ctypes.byref(a), ctypes.byref(b)) == -1
+
+
 def test_shard_weight_slices_codes_and_scales_consistently():
     _, W = inputs.make_inputs(128, 512, 256)
     wq, sw = oquant.quant_fp8_128x128(W)
@@ -69,6 +83,10 @@ def _worker(rank, world, port, out_dir):
         assert got is out and torch.equal(out, full)
         got2 = sharded.gemm_a8w8_blockscale(aq, wq_r, C_r, sa, sw_r, gather=True, gemm_fn=_oracle_gemm)
         assert torch.equal(got2, full) and got2.is_contiguous()
+        # blocked form: what the collective produces, block r = rank r's columns, no re-tiling copy
+        blocked = sharded.gemm_a8w8_blockscale(aq, wq_r, C_r, sa, sw_r, gather="blocked", gemm_fn=_oracle_gemm)
+        assert blocked.shape == (world, 128, 512 // world)
+        assert all(torch.equal(blocked[r], full[:, r * (512 // world):(r + 1) * (512 // world)]) for r in range(world))
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
