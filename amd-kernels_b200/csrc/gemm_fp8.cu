@@ -121,8 +121,10 @@ struct GemmParams {
 // behind the barriers holds, per epilogue thread and for two chunks of kScaleChunk K blocks, the
 // activation scales of the thread's row (thread-private float4 slots) and, per epilogue warp, the
 // chunk's weight scales.
-constexpr int kScaleChunk = 32;       // K blocks per chunk of staged scales (at most 32: one lane per K block; 8 and 16 measured slower or equal)
-template <int BN, int STAGES, bool kPair = false, int AROWS = BM, int SCALE_THREADS = 0>
+// kScaleChunk: K blocks per chunk of staged scales (at most 32: one lane per K block; 32 by default, 8 measured
+// slower and 16 equal; the scatter kernels take 16 to make room for their output staging).
+// kStageOut: bytes behind the scales in which the epilogue warps transpose their output block (scatter mode).
+template <int BN, int STAGES, bool kPair = false, int AROWS = BM, int SCALE_THREADS = 0, int kScaleChunk = 32, int kStageOut = 0>
 struct SmemLayout {
     static constexpr int kABytes = AROWS * BK;
     static constexpr int kTailPad = (BM - AROWS) * BK;
@@ -136,7 +138,8 @@ struct SmemLayout {
     static constexpr int kSaBytes = 2 * (kScaleChunk / 4) * SCALE_THREADS * 16;     // [2][chunk/4][thread] float4
     static constexpr int kSbBytes = 2 * (SCALE_THREADS / 32) * kScaleChunk * 4;     // [2][warp][chunk] float
     static constexpr int kScaleBytes = kSaBytes + kSbBytes;
-    static constexpr int kTotal = SCALE_THREADS > 0 ? kScaleOffset + kScaleBytes
+    static constexpr int kStageOutOffset = ((kScaleOffset + kScaleBytes + 127) / 128) * 128;
+    static constexpr int kTotal = kStageOut > 0 ? kStageOutOffset + kStageOut : SCALE_THREADS > 0 ? kScaleOffset + kScaleBytes
                                                     : kBarOffset + (kNumBars * 8 + 16 > kTailPad ? kNumBars * 8 + 16 : kTailPad);
     static constexpr int kDynamic = kTotal + 1024;   // slack for the manual 1024-byte alignment
     static_assert(kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
@@ -233,7 +236,9 @@ template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false,
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     constexpr int EPI_GROUPS = (BN == 256) ? 2 : 1;     // groups of 4 warps; each owns BN/EPI_GROUPS columns
-    using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0>;
+    constexpr int kScaleChunk = kOut == 1 ? 16 : 32;
+    constexpr int kStageOut = kOut == 1 ? 4 * EPI_GROUPS * 4096 : 0;       // 32 rows x 128 bytes per epilogue warp
+    using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0, kScaleChunk, kStageOut>;
     constexpr bool kGrouped = kOut == 3;
     static_assert(!kGrouped || (kBlockScale && kGn128 && !kPair), "grouped mode: block scales, 128-column groups, one CTA");
     static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
@@ -601,7 +606,37 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                     sbuf ^= 1;
                 }
-                if (ok && row_ok) {
+                if constexpr (kOut == 1) {
+                    // Scatter mode: the copies in the other GPUs' memory travel over NVLink, where a 32-byte store per
+                    // lane and row wastes most of every packet.  The warp transposes its 32 x 128 block through shared
+                    // memory, 64 columns at a time, so that eight lanes write 128 contiguous bytes of one row.
+                    if (ok) {
+                        uint8_t* const stg = smem + L::kStageOutOffset + ew * 4096;
+                        const int wrow0 = (row - row_in_tile) + quarter * 32;          // first row of this warp's block
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                const float2 a0 = acc2[32 * h + 4 * c], a1 = acc2[32 * h + 4 * c + 1], a2 = acc2[32 * h + 4 * c + 2], a3 = acc2[32 * h + 4 * c + 3];
+                                *reinterpret_cast<uint4*>(stg + lane * 128 + ((c ^ (lane & 7)) * 16)) =
+                                    make_uint4(pack_bf16(a0.x, a0.y), pack_bf16(a1.x, a1.y), pack_bf16(a2.x, a2.y), pack_bf16(a3.x, a3.y));
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int rr = 4 * i + (lane >> 3), cc = lane & 7;
+                                const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((cc ^ (rr & 7)) * 16));
+                                const int grow = wrow0 + rr;
+                                if (grow < p.M) {
+                                    const int64_t off = (int64_t)grow * p.ldc + col_base + 64 * h + 8 * cc;
+                                    *reinterpret_cast<uint4*>(p.C + off) = v;
+                                    for (int d = 0; d < p.n_peer; ++d) *reinterpret_cast<uint4*>(p.peer[d] + off) = v;
+                                }
+                            }
+                            __syncwarp();
+                        }
+                    }
+                } else if (ok && row_ok) {
                     // N % 128 == 0 in block-scale mode: rows are 32-byte aligned, whole groups are in range
 #pragma unroll
                     for (int c = 0; c < 128; c += 16) {
@@ -623,10 +658,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             store_bf16x16(split_cat_ptr(p, row, col_base + c), v);
                         } else {
                             store_bf16x16(crow + col_base + c, v);
-                            if constexpr (kOut == 1) {
-                                for (int d = 0; d < p.n_peer; ++d)      // other GPUs' copies: posted stores over NVLink
-                                    store_bf16x16(p.peer[d] + (int64_t)row * p.ldc + col_base + c, v);
-                            }
                         }
                     }
                 }
@@ -783,7 +814,8 @@ inline bool skinny_enabled() {
 
 template <int BN, int STAGES, bool kBlockScale, bool kGn128 = false, int AROWS = BM, int kOut = 0>
 int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t st) {
-    using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0>;
+    using L = SmemLayout<BN, STAGES, false, AROWS, (kBlockScale && kGn128) ? (BN == 256 ? 256 : 128) : 0, kOut == 1 ? 16 : 32,
+                         kOut == 1 ? (BN == 256 ? 8 : 4) * 4096 : 0>;
     static_assert(L::kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
     auto kern = gemm_fp8_kernel<BN, STAGES, kBlockScale, kGn128, false, AROWS, kOut>;
     // the attribute is per device; set it on every call (cheap) so multi-device processes work
