@@ -935,8 +935,12 @@ def main():
                 "value": flops_of(wl.kind, 1, wl.M, wl.N_total, wl.K) / 1e12 / (fg_ms / 1e3), "unit": "TFLOP/s",
                 "ms_per_step": fg_ms, "bytes_out_per_rank": bytes_in, "nvlink_gbs_out_per_rank": bytes_in / 1e9 / (fg_ms / 1e3),
                 "bit_equal_to_shards": same,
-                "how": "the GEMM's epilogue stores every finished tile into all ranks' [M, N] (plain st.global to peer-mapped memory), "
-                       "then a one-element all-reduce as the barrier; no collective moves data"}
+                "roofline": {"target_ms": max(dom_ms, bytes_in / 770e9 * 1e3), "frac": max(dom_ms, bytes_in / 770e9 * 1e3) / fg_ms,
+                             "how": "target = the slower of the GEMM alone (measured above) and bytes_out / 770 GB/s "
+                                    "(measured peer-copy rate per direction)"},
+                "how": "the GEMM's epilogue transposes each warp's 32x128 block through shared memory and stores 128-byte rows "
+                       "into all ranks' [M, N] (plain st.global to peer-mapped memory), then a one-element all-reduce as the "
+                       "barrier; no collective moves data"}
             del peer, shards, theirs
         except Exception as e:                             # symmetric memory unavailable: report, keep the line
             extras["gemm_fused_gather"] = {"error": f"{type(e).__name__}: {e}"[:300]}
