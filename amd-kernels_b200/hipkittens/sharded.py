@@ -13,6 +13,31 @@ import torch
 import torch.distributed as dist
 
 
+def bind_host_to_gpu(device):
+    """Restrict the calling process to the CPU cores NVML reports as nearest to ``device`` (same socket /
+    NUMA node), so that pinned host buffers allocated afterwards are local to the GPU's PCIe root: with one
+    process per GPU, uploads and downloads then do not cross the inter-socket link.  Only the process's
+    own CPU affinity changes (``os.sched_setaffinity``); NVML is read, nothing on the GPU is set.
+    Returns the sorted core list, or ``None`` when NVML has no answer or the cores are not available to
+    this process (the affinity is then left as it was)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device).uuid)
+        h = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        near = {64 * w + b for w, bits in enumerate(words) for b in range(64) if (int(bits) >> b) & 1}
+        cores = sorted(near & os.sched_getaffinity(0))
+        if not cores:
+            return None
+        os.sched_setaffinity(0, cores)
+        return cores
+    except Exception:
+        return None
+
+
 def shard_bounds(N, world_size, rank, align=128):
     """Column range [n0, n1) of ``rank``: N is cut into ``align``-wide blocks which are dealt out
     as evenly as possible (the first ``blocks % world_size`` ranks get one more)."""

@@ -806,6 +806,10 @@ def main():
         return 1
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    near_cores, all_cores = None, os.sched_getaffinity(0)
+    if os.environ.get("HKB_BENCH_NO_BIND", "0") != "1":
+        from hipkittens import sharded as _sh
+        near_cores = _sh.bind_host_to_gpu(dev)       # pinned buffers below come from the GPU's own NUMA node
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -1002,6 +1006,7 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        os.sched_setaffinity(0, all_cores)           # the CPU arm may use every core the process was given
         rows = default_sample_rows(name)
         cpu_reference_step(name, rows)
         tot, u_tot, reps = 0.0, 0.0, 0
@@ -1022,6 +1027,9 @@ def main():
                "data": "synthetic", "config": config_of(name, world),
                "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
                "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks}
+        if e2e is not None:
+            e2e["host_cores"] = (f"{len(near_cores)} cores nearest the GPU (NVML affinity), pinned buffers allocated from there"
+                                 if near_cores else "process affinity unchanged")
         out.update(extras)
         print(json.dumps(out), flush=True)
     if world > 1:

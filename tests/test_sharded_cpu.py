@@ -109,3 +109,13 @@ def test_gather_layout_is_column_blocks_in_rank_order():
     for r in range(g):
         assert torch.equal(full[:, r * n:(r + 1) * n], blocked[r])
     assert np.array_equal(full[0].numpy(), [0, 1, 6, 7, 12, 13, 18, 19])
+
+
+def test_bind_host_to_gpu_leaves_affinity_alone_without_a_gpu():
+    before = os.sched_getaffinity(0)
+    got = sharded.bind_host_to_gpu(torch.device("cuda", 0))
+    if not torch.cuda.is_available():
+        assert got is None and os.sched_getaffinity(0) == before
+    else:
+        assert got is None or set(got) <= before
+    os.sched_setaffinity(0, before)
