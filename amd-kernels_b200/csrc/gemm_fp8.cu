@@ -109,7 +109,15 @@ struct GemmParams {
     uint32_t* status;
     uint64_t wait_ns;          // limit of every mbarrier wait (kWaitLimitNs in production)
     int skip_kblock;           // >= 0: the producer leaves this K block of its first tile unloaded (wait-limit probe only)
+    unsigned long long* trace; // timeline build (kOut == 4) only: [grid][kTraceEvents][kTraceKb] SM clock readings
 };
+
+// Timeline build of the block-scale kernel: every CTA records, for the first kTraceKb K blocks of its third tile,
+// when (SM clock) the MMA thread saw the operands (event 0), issued the MMAs (1) and had them issued (3), when the
+// producer got the stage back (2), and when each of the eight epilogue warps released the accumulator buffer
+// (4 + warp) and saw the partial product (12 + warp).
+constexpr int kTraceEvents = 20;
+constexpr int kTraceKb = 64;
 
 // kPair: two CTAs (a cluster of 2) share one 256 x BN tile; each stages its own 128 rows of A
 // and its own half of B's BN rows.
@@ -231,7 +239,8 @@ __device__ __forceinline__ float2 ffma2(uint32_t a0, uint32_t a1, float2 s, floa
 // kOut (block-scale): 0 = plain [M, N] result; 1 = the result also goes to p.n_peer further destinations
 // (the other GPUs' copies of the assembled output; 128-column weight-scale groups only); 2 = split-cat;
 // 3 = grouped (MoE): the M tiles come from a device-side list (expert, block), weights, weight scales and the
-// fp32 bias are per expert, rows of A / C are sorted by expert (128-column weight-scale groups only).
+// fp32 bias are per expert, rows of A / C are sorted by expert (128-column weight-scale groups only);
+// 4 = plain result plus the hand-off timeline in p.trace (diagnostic build, same code otherwise).
 template <int BN, int STAGES, bool kBlockScale, bool kGn128, bool kPair = false, int AROWS = BM, int kOut = 0>
 __global__ void __launch_bounds__(gemm_threads<BN, kBlockScale, kPair>(), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -240,6 +249,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     constexpr int kStageOut = kOut == 1 ? 4 * EPI_GROUPS * 4096 : 0;       // 32 rows x 128 bytes per epilogue warp
     using L = SmemLayout<BN, STAGES, kPair, AROWS, (kBlockScale && kGn128) ? 128 * EPI_GROUPS : 0, kScaleChunk, kStageOut>;
     constexpr bool kGrouped = kOut == 3;
+    constexpr bool kTrace = kOut == 4;
     static_assert(!kGrouped || (kBlockScale && kGn128 && !kPair), "grouped mode: block scales, 128-column groups, one CTA");
     static_assert(!kPair || BN == 256, "CTA pairs work on 256 x 256 tiles");
     constexpr int EPI_WARPS = 4 * EPI_GROUPS;
@@ -268,6 +278,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int kblocks = p.K / BK;
+    auto trace_at = [&](int ev, int kb, bool on, long long clk) {
+        if constexpr (kTrace) {
+            if (on && kb < kTraceKb) p.trace[((size_t)blockIdx.x * kTraceEvents + ev) * kTraceKb + kb] = (unsigned long long)clk;
+        }
+    };
     // pair mode: p.m_blks counts 256-row blocks, a "tile" belongs to the cluster, CTA `rank` owns
     // rows [rank*128, rank*128+128) of it and stages rows [rank*128, ..) of the tile's B block
     const uint32_t rank = kPair ? cluster_ctarank() : 0u;
@@ -329,6 +344,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, kErrWaitProducer, p.wait_ns)) { ok = false; break; }
+                    if constexpr (kTrace) trace_at(2, kb, t == tile0 + 2 * tile_step, clock64());
                     const uint32_t sa = smem_base + s * L::kStageBytes;
                     if (p.skip_kblock == kb && t == tile0) {
                         // wait-limit probe: nothing is loaded and nothing will arrive on this stage's barrier
@@ -371,6 +387,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     // what this thread really waits for.  So: operands first, descriptors ready, then the buffer, and
                     // the MMAs go out right behind it.
                     if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
+                    // timeline: the readings stay in registers until the MMAs are out (a store here would sit in front of them)
+                    const long long tr_full = kTrace ? clock64() : 0;
                     const uint32_t sa = smem_base + s * L::kStageBytes;
                     const uint64_t da = smem_desc_sw128(sa);
                     const uint64_t db = smem_desc_sw128(sa + L::kABytes);
@@ -379,6 +397,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         if (!mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, kErrWaitMma, p.wait_ns)) { ok = false; break; }
                     }
                     tc_fence_after();
+                    const long long tr_issue = kTrace ? clock64() : 0;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint32_t accumulate = kBlockScale ? (k != 0) : ((kb | k) != 0);
@@ -393,6 +412,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     // smem stage free once these MMAs retire (pair mode: in both CTAs)
                     if constexpr (kPair) tc_commit_pair(empty_bar(s), 3); else tc_commit(empty_bar(s));
+                    if constexpr (kTrace) {
+                        const bool on = t == tile0 + 2 * tile_step;
+                        trace_at(0, kb, on, tr_full);
+                        trace_at(1, kb, on, tr_issue);
+                        trace_at(3, kb, on, clock64());
+                    }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (!kBlockScale && ok) {
@@ -572,6 +597,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (sub == 3 && kk + 1 < kb_end) sa4 = sa_s[(size_t)((kk + 1) >> 2) * EPI_THREADS];
                     if (!__all_sync(0xFFFFFFFFu, mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, kErrWaitEpilogue, p.wait_ns))) { ok = false; break; }
                     tc_fence_after();
+                    if constexpr (kTrace) trace_at(12 + ew, ch * kScaleChunk + kk, lane == 0 && t == tile0 + 2 * tile_step, clock64());
                     const uint32_t t_addr = tmem_base + lane_addr + acc * BN + grp * COLS_PER_GROUP;
                     uint32_t ra[32], rb[32];
                     // the partial product lives in registers after the fourth load: the TMEM buffer goes back
@@ -600,6 +626,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int j = 0; j < 16; ++j) acc2[32 + j] = ffma2(ra[2 * j], ra[2 * j + 1], s2, acc2[32 + j]);
                     tmem_ld_wait32(rb);
                     release();
+                    if constexpr (kTrace) trace_at(4 + ew, ch * kScaleChunk + kk, lane == 0 && t == tile0 + 2 * tile_step, clock64());
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc2[48 + j] = ffma2(rb[2 * j], rb[2 * j + 1], s2, acc2[48 + j]);
                     if (++acc == 2) { acc = 0; acc_ph ^= 1; }
@@ -829,6 +856,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
     note_kernel(kOut == 1 ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,scatter>" : "gemm_fp8_kernel<128,blockscale,scatter>") :
                 kOut == 2 ? (kGn128 ? "gemm_fp8_kernel<128,blockscale,split_cat>" : "gemm_fp8_kernel<128,blockscale,gn1,split_cat>") :
                 kOut == 3 ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale,grouped>" : "gemm_fp8_kernel<128,blockscale,grouped>") :
+                kOut == 4 ? "gemm_fp8_kernel<256,blockscale,timeline>" :
                 kBlockScale ? (BN == 256 ? "gemm_fp8_kernel<256,blockscale>" : kGn128 ? "gemm_fp8_kernel<128,blockscale>" : "gemm_fp8_kernel<128,blockscale,gn1>")
                             : (BN == 256 ? "gemm_fp8_kernel<256,pts>" : BN == 128 ? "gemm_fp8_kernel<128,pts>" : "gemm_fp8_kernel<64,pts>"));
     return check_launch("gemm_fp8_kernel");
@@ -850,7 +878,8 @@ int common_checks(const char* who, const void* A, const void* B, const void* C, 
 struct SplitCat { void* c2; int64_t s1, s2, s3; };      // C is c1 [M, D, s1+s3], c2 [M, D, s2], N = D*(s1+s2)
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                              const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream,
-                             int64_t ldc = 0, void* const* peers = nullptr, int n_peer = 0, const SplitCat* sc = nullptr);
+                             int64_t ldc = 0, void* const* peers = nullptr, int n_peer = 0, const SplitCat* sc = nullptr,
+                             unsigned long long* trace = nullptr);
 
 // wait_ns / skip_kblock: production passes kWaitLimitNs / -1; the wait-limit probe a short limit
 // and a K block that the producer leaves unloaded.
@@ -929,6 +958,19 @@ int hkb_debug_gemm_fp8_wait_probe(const void* A, const void* B, void* C, const f
 int hkb_gemm_fp8_blockscale(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                             int64_t M, int64_t N, int64_t K, void* stream) {
     return hkb::gemm_fp8_blockscale_impl(A, B, C, sa, sb, gn, nullptr, nullptr, M, N, K, stream);
+}
+
+int hkb_debug_gemm_fp8_blockscale_timeline(const void* A, const void* B, void* C, const float* sa, const float* sb,
+                                           int64_t M, int64_t N, int64_t K, void* trace, int64_t trace_bytes, void* stream) {
+    using namespace hkb;
+    HKB_REQUIRE(trace && (reinterpret_cast<uintptr_t>(trace) & 7) == 0, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale timeline: trace buffer must be non-null and 8-byte aligned");
+    const int sms = sm_count();
+    HKB_REQUIRE(sms > 0, HKB_ERR_CUDA, "no CUDA device");
+    const int64_t need = (int64_t)sms * kTraceEvents * kTraceKb * 8;
+    HKB_REQUIRE(trace_bytes >= need, HKB_ERR_BAD_ARG, "gemm_fp8_blockscale timeline: trace buffer has %lld bytes, %lld needed", (long long)trace_bytes, (long long)need);
+    const cudaError_t e = cudaMemsetAsync(trace, 0, (size_t)need, (cudaStream_t)stream);
+    HKB_REQUIRE(e == cudaSuccess, HKB_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+    return gemm_fp8_blockscale_impl(A, B, C, sa, sb, 128, nullptr, nullptr, M, N, K, stream, 0, nullptr, 0, nullptr, (unsigned long long*)trace);
 }
 
 int hkb_gemm_fp8_blockscale_scatter(const void* A, const void* B, void* const* C_dst, int n_dst, int64_t ldc,
@@ -1017,7 +1059,7 @@ namespace hkb {
 
 int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float* sa, const float* sb, int64_t gn,
                              const void* c_a, const void* c_b, int64_t M, int64_t N, int64_t K, void* stream,
-                             int64_t ldc, void* const* peers, int n_peer, const SplitCat* sc) {
+                             int64_t ldc, void* const* peers, int n_peer, const SplitCat* sc, unsigned long long* trace) {
     int rc = common_checks("gemm_fp8_blockscale", A, B, C, 1, M, N, K);
     if (rc != HKB_OK) return rc;
     if (sc) {
@@ -1059,8 +1101,17 @@ int gemm_fp8_blockscale_impl(const void* A, const void* B, void* C, const float*
     CUtensorMap tmA, tmB;
     rc = make_tmap_bytes(&tmA, A, (uint64_t)K, (uint64_t)M, 1, BM);
     if (rc != HKB_OK) return rc;
-    // CTA pairs do not pay off here: the per-K-block accumulator hand-off would cross the cluster
-    // (measured ~2x slower than the single-CTA kernel); kept reachable for experiments only.
+    if (trace) {
+        HKB_REQUIRE(bn == 256 && !c_a && n_peer == 0 && ldc == N, HKB_ERR_UNSUPPORTED,
+                    "gemm_fp8_blockscale timeline: needs the 256-wide kernel (gn = 128, N %% 256 == 0, at least two tiles per SM) and the plain epilogue");
+        p.trace = trace;
+        rc = make_tmap_bytes(&tmB, B, (uint64_t)K, (uint64_t)N, 1, 256);
+        if (rc != HKB_OK) return rc;
+        return launch_gemm<256, 3, true, true, BM, 4>(tmA, tmB, p, st);
+    }
+    // CTA pairs: the per-K-block accumulator hand-off crosses the cluster.  With a relaxed remote arrive it runs within
+    // 2-3 % of the single-CTA kernel (with a release at cluster scope it was 1.9x slower), never ahead of it: kept
+    // reachable for experiments only.
     static const bool bs_pairs = [] { const char* v = getenv("HKB_BLOCKSCALE_PAIRS"); return v && v[0] == '1'; }();
     const int64_t pair_tiles = ((M + 255) / 256) * (N / 256);
     if (bs_pairs && bn == 256 && M > 128 && pair_tiles >= sms / 2) {

@@ -351,6 +351,29 @@ void blockscale(py::object A_, py::object B_, py::object C_, py::object sa_, py:
     check(hkb_gemm_fp8_blockscale_scatter(A.ptr, B.ptr, dst.data(), (int)dst.size(), ldc, (const float*)sa.ptr,
                                           (const float*)sb.ptr, M, N, K, L.stream));
 }
+// Diagnostic: the block-scale GEMM from the timeline build; `trace` is an int64 / uint64 CUDA tensor of at least
+// SMs * 20 * 64 elements that receives the per-K-block clock readings (layout in the C header).
+[[maybe_unused]] void dispatch_blockscale_timeline(py::object A_, py::object B_, py::object C_, py::object sa_, py::object sb_,
+                                                   py::object trace_) {
+    TView A = view(A_, "A"), B = view(B_, "B"), C = view(C_, "C"), sa = view(sa_, "a_scale"), sb = view(sb_, "b_scale");
+    TView tr = view(trace_, "trace");
+    want_dtype(A, "A", {"float8_e4m3fn", "uint8"});
+    want_dtype(B, "B", {"float8_e4m3fn", "uint8"});
+    want_dtype(C, "C", {"bfloat16"});
+    want_dtype(sa, "a_scale", {"float32"});
+    want_dtype(sb, "b_scale", {"float32"});
+    want_dtype(tr, "trace", {"int64", "uint64"});
+    if (A.rank() != 2 || B.rank() != 2 || A.dim(1) != B.dim(1)) fail("A [M, K] and B [N, K] must be 2-D with the same K");
+    const int64_t M = A.dim(0), K = A.dim(1), N = B.dim(0);
+    if (K % 128 || N % 128) fail("K and N must be multiples of 128");
+    if (C.numel != M * N) fail("C must be [M, N]");
+    if (sa.numel != M * (K / 128)) fail("a_scale must be [M, K/128]");
+    if (sb.numel != (K / 128) * (N / 128)) fail("b_scale must be [K/128, N/128]");
+    same_device({&A, &B, &C, &sa, &sb, &tr});
+    Launch L(A.device);
+    check(hkb_debug_gemm_fp8_blockscale_timeline(A.ptr, B.ptr, C.ptr, (const float*)sa.ptr, (const float*)sb.ptr, M, N, K,
+                                                 tr.ptr, tr.numel * 8, L.stream));
+}
 // fused_gemm_a8w8_blockscale_mul_add_tk.dispatch(a, b, c, a_scale, b_scale, c_a, c_b):
 // kernels/gemm-fused/fused_gemm_a8w8_blockscale_mul_add/kernel.cpp:184-193.  C = c_a * gemm + c_b.
 [[maybe_unused]] void dispatch_blockscale_mul_add(py::object A, py::object B, py::object C, py::object sa, py::object sb,
@@ -644,6 +667,7 @@ PYBIND11_MODULE(HKB_SHIM_NAME, m) {
     m.doc() = "FP8 GEMM with 1x128 activation and 128x128 (or 128x1) weight block scales, sm_100a tcgen05";
     m.def("dispatch", &dispatch_blockscale, "A"_a, "B"_a, "C"_a, "a_scale"_a, "b_scale"_a);
     m.def("dispatch_scatter", &dispatch_blockscale_scatter, "A"_a, "B"_a, "dst_ptrs"_a, "ldc"_a, "a_scale"_a, "b_scale"_a);
+    m.def("dispatch_timeline", &dispatch_blockscale_timeline, "A"_a, "B"_a, "C"_a, "a_scale"_a, "b_scale"_a, "trace"_a);
 #elif defined(HKB_SHIM_GEMM_AFP4WFP4)
     m.doc() = "MXFP4 x MXFP4 GEMM (e2m1 codes, e8m0 scales per 32), sm_100a tcgen05 block-scaled MMA";
     m.def("dispatch", &dispatch_mxfp4, "A"_a, "B"_a, "C"_a, "a_scales"_a = py::none(), "b_scales"_a = py::none());

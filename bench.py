@@ -78,6 +78,7 @@ WORKLOADS = {
     "qbw-moe-mxfp8": ("quant-moe-mxfp8", 1, 16384, 0, 8192),
     "qbw-moe-mxfp4": ("quant-moe-mxfp4", 1, 16384, 0, 8192),
     "qbw-moe-up8": ("quant-moe-up8", 1, 16384, 0, 8192),
+    "timeline": ("timeline", 1, 4096, 14336, 8192),  # c5s through the diagnostic build: per-K-block hand-off times, not a throughput line
     "peak-fp8": ("peak", 1, 0, 0, 0),
     "peak-fp4": ("peak", 1, 0, 0, 0),
 }
@@ -632,6 +633,49 @@ def run_peak(args, name, dev):
     print(json.dumps(out), flush=True)
 
 
+def run_timeline(args, dev):
+    """`--workload timeline`: the block-scale GEMM of `c5s` from the build that records, per CTA and K block, when
+    the MMA thread saw the operands / issued the MMAs and when each epilogue warp saw and released the partial
+    product (SM clocks).  Prints medians over CTAs and K blocks 8..55 of each CTA's third tile."""
+    import numpy as np
+    import hipkittens as hk
+    wl = Workload("c5s", 0, 1, dev)
+    wl.step()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    trace = torch.zeros(sms, 20, 64, dtype=torch.int64, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for _ in range(3):
+        hk.gemm.a8w8_blockscale.dispatch_timeline(wl.Aq, wl.Wq, wl.C, wl.sa, wl.sw, trace)
+    ev[0].record()
+    hk.gemm.a8w8_blockscale.dispatch_timeline(wl.Aq, wl.Wq, wl.C, wl.sa, wl.sw, trace)
+    ev[1].record()
+    torch.cuda.synchronize()
+    ms = ev[0].elapsed_time(ev[1])
+    t = trace.cpu().numpy()
+    kb = np.arange(8, 56)
+    full, issue, issued, prod = t[:, 0], t[:, 1], t[:, 3], t[:, 2]
+    rel, seen = t[:, 4:12], t[:, 12:20]
+    first_seen, last_seen = seen.min(1), seen.max(1)
+    first_rel, last_rel = rel.min(1), rel.max(1)
+    late = (seen - first_seen[:, None, :])[:, :, kb].mean(2)          # [cta, warp]: how long after the first warp
+    med = lambda a: float(np.median(a))
+    out = {"workload": "timeline", "shape": [wl.M, wl.N_total, wl.K], "kernel": hk.last_kernel(), "ms": ms,
+           "tflops": flops_of("blockscale", 1, wl.M, wl.N_total, wl.K) / 1e12 / (ms / 1e3), "unit": "SM clocks, median over CTAs and K blocks 8..55",
+           "period_per_kblock": med(np.diff(issue[:, 8:56], axis=1)),
+           "operands_ready_before_issue": med((issue - full)[:, kb]),
+           "issue_to_first_warp_sees_partial": med((first_seen - issue)[:, kb]),
+           "issue_to_issued": med((issued - issue)[:, kb]),
+           "last_warp_sees_after_first": med((last_seen - first_seen)[:, kb]),
+           "drain_first_warp": med((first_rel - first_seen)[:, kb]),
+           "last_release_after_first": med((last_rel - first_rel)[:, kb]),
+           "last_release_to_next_issue_same_buffer": med((issue[:, 10:58] - last_rel[:, 8:56])),
+           "next_issue_after_partial_seen": med((issue[:, 9:57] - first_seen[:, 8:56])),
+           "stage_back_to_operands_seen": med((full[:, 11:59] - prod[:, 11:59])),
+           "warp_lateness_by_quarter": [round(float(np.median(late[:, [q, q + 4]])), 1) for q in range(4)],
+           "note": "warps of quarter q run on scheduler q; the MMA-issuing warp is on scheduler 1, the TMA producer on scheduler 0"}
+    print(json.dumps(out), flush=True)
+
+
 def shard_check(wl, nrows=64):
     """Untimed: `nrows` sampled rows of this rank's output shard against an fp32 evaluation of the
     same block-scale sum on the device (torch, K block by K block).  Returns max|C-ref| / max|ref|."""
@@ -815,6 +859,13 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    if WORKLOADS[name][0] == "timeline":
+        if rank == 0:
+            run_timeline(args, dev)
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return 0
     if WORKLOADS[name][0] == "peak":
         if rank == 0:
             run_peak(args, name, dev)

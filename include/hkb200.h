@@ -55,6 +55,18 @@ int hkb_debug_gemm_fp8_wait_probe(const void* A, const void* B, void* C, const f
                                   const float* sb, int64_t M, int64_t N, int64_t K,
                                   uint64_t wait_limit_ns, void* stream);
 
+/* Timeline of the block-scale GEMM's per-K-block hand-off: hkb_gemm_fp8_blockscale (gn = 128, a problem
+ * that takes the 256-wide kernel: N % 256 == 0 and at least two tiles per SM) run from a build of the same
+ * kernel in which every CTA records SM-clock readings for the first 64 K blocks of its third tile into
+ * trace, a device array u64 [SMs][20][64] (zeroed by the call; trace_bytes >= SMs * 20 * 64 * 8):
+ * event 0 MMA thread saw the operands, 1 issued the K block's MMAs, 3 had them issued, 2 the producer got the
+ * stage back, 4 + w epilogue warp w released the accumulator buffer, 12 + w epilogue warp w saw the partial
+ * product.  C receives the same result as hkb_gemm_fp8_blockscale.  For tuning; no counterpart in the
+ * reference project. */
+int hkb_debug_gemm_fp8_blockscale_timeline(const void* A, const void* B, void* C, const float* sa,
+                                           const float* sb, int64_t M, int64_t N, int64_t K,
+                                           void* trace, int64_t trace_bytes, void* stream);
+
 /* Tensor-core ceiling probe: every SM issues `batches` x 4 back-to-back tcgen05.mma instructions
  * (kind 0: FP8 e4m3, 128 x 256 x 32 each; kind 1: MXFP4 block-scaled, 128 x 256 x 64 each) on
  * operand tiles resident in shared memory; no loads or stores in the loop.  The caller times the

@@ -636,6 +636,44 @@ def test_blockscale_result_scattered_into_column_slabs_of_wider_matrices(hk, sha
     _check(plain, gemm.gemm_fp8_blockscale(aq, bq, sa, sb), f"blockscale scatter {shape}")
 
 
+def test_blockscale_timeline_build_gives_the_same_result_and_ordered_clock_readings(hk):
+    """The diagnostic build of the 256-wide block-scale kernel: bit-equal output, and for every CTA's third
+    tile the per-K-block readings come in the order the hand-off imposes: operands seen <= MMAs issued <
+    first epilogue warp sees the partial < that warp releases the buffer; a buffer's next MMAs are issued
+    after its last release."""
+    M, N, K = 2048, 7168, 1024                   # 16 x 28 = 448 tiles: three per CTA on 148 SMs
+    aq, bq, _, _ = _fp8_operands(M, N, K, seed=77)
+    g = torch.Generator().manual_seed(3)
+    sa = torch.rand(M, K // 128, generator=g) * 0.1 + 0.01
+    sb = torch.rand(K // 128, N // 128, generator=g) * 0.1 + 0.01
+    d = [_dev(aq), _dev(bq), _dev(sa), _dev(sb)]
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(d[0], d[1], plain, d[2], d[3])
+    assert hk.last_kernel() == "gemm_fp8_kernel<256,blockscale>"
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    traced = torch.empty_like(plain)
+    trace = torch.full((sms, 20, 64), -1, dtype=torch.int64, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch_timeline(d[0], d[1], traced, d[2], d[3], trace)
+    assert "timeline" in hk.last_kernel()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.equal(traced, plain)
+    t = trace.cpu().numpy()
+    kbs = K // 128
+    ctas = [c for c in range(sms) if c + 2 * sms < 448]
+    assert len(ctas) >= 100
+    for c in ctas:
+        full, issue, issued = t[c, 0, :kbs], t[c, 1, :kbs], t[c, 3, :kbs]
+        rel, seen = t[c, 4:12, :kbs], t[c, 12:20, :kbs]
+        assert (t[c, :, :kbs] > 0).all() and (t[c, :, kbs:] == 0).all()
+        assert (full <= issue).all() and (issue < issued).all()
+        assert (issue < seen.min(0)).all() and (seen < rel).all()
+        assert (issue[2:] > rel.max(0)[:-2]).all()          # two accumulator buffers
+    with pytest.raises(RuntimeError):                        # a problem that takes the 128-wide kernel has no timeline build
+        small = torch.empty(256, 512, dtype=torch.bfloat16, device=DEV)
+        hk.gemm.a8w8_blockscale.dispatch_timeline(d[0][:256], d[1][:512], small, d[2][:256], _dev(sb[:, :4].contiguous()), trace)
+
+
 def test_config5_single_gpu_shard_shape_sampled_rows(hk):
     """Config 5's per-GPU problem at 8 GPUs (16384 x 7168 x 8192: one rank's column shard), config 5's
     distributions; the oracle checks 64 sampled rows."""
