@@ -611,6 +611,54 @@ def test_config2_full_size_sampled_rows(hk):
     _check(C[rows], ref, "config 2 full size, sampled rows")
 
 
+def _blockscale_all_elements_vs_device_fp32(hk, M, N, K, what, col_chunk):
+    """Every element of the block-scale GEMM against an fp32 evaluation on the device (torch matmul with TF32 off,
+    a checker only): C = (codes_a * sa per 128-K block) @ (codes_w * sb per 128 x 128 block)^T, N in chunks.
+    Also the exact property that doubling a_scale doubles every bf16 output bit for bit."""
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, K // 128, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(K // 128, N // 128, device=DEV)
+    hk.fused_rmsnorm_fp8_quant_fwd(A, None, aq, sa, 1e-6)
+    hk.weight_quant_128x128(W, wq, sw)
+    del A, W
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_blockscale.dispatch(aq, wq, C, sa, sw)
+    assert hk.last_kernel() == "gemm_fp8_kernel<256,blockscale>"
+    C2 = torch.empty_like(C)
+    hk.gemm.a8w8_blockscale.dispatch(aq, wq, C2, sa * 2.0, sw)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.equal(C2, C * 2.0), f"{what}: doubling a_scale must double every output exactly"
+    del C2
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        a_deq = aq.view(torch.float8_e4m3fn).float() * sa.repeat_interleave(128, dim=1)
+        worst, peak = 0.0, 0.0
+        for n0 in range(0, N, col_chunk):
+            n1 = min(N, n0 + col_chunk)
+            w_deq = wq[n0:n1].view(torch.float8_e4m3fn).float()
+            w_deq *= sw[:, n0 // 128:(n1 + 127) // 128].repeat_interleave(128, dim=1)[:, :n1 - n0].t().repeat_interleave(128, dim=1)
+            ref = a_deq @ w_deq.t()
+            worst = max(worst, float((C[:, n0:n1].float() - ref).abs().max()))
+            peak = max(peak, float(ref.abs().max()))
+            del w_deq, ref
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+    assert worst / peak <= TOL, f"{what}: max |C - ref| / max |ref| = {worst / peak:.3e}"
+
+
+def test_config2_full_size_every_element_vs_device_fp32(hk):
+    _blockscale_all_elements_vs_device_fp32(hk, 4096, 14336, 4096, "config 2", 14336)
+
+
+def test_config5_full_size_every_element_vs_device_fp32(hk):
+    """Config 5 on one GPU (16384 x 57344 x 8192, 0.94 G outputs), the reference matmul in eight column chunks."""
+    _blockscale_all_elements_vs_device_fp32(hk, 16384, 57344, 8192, "config 5", 7168)
+
+
 @pytest.mark.parametrize("shape", [(384, 512, 512), (2304, 4608, 256)])      # 128-wide and 256-wide tile kernels
 def test_blockscale_result_scattered_into_column_slabs_of_wider_matrices(hk, shape):
     """The multi-GPU form of the GEMM on one device: the [M, N] result goes into columns [col0, col0+N)
@@ -784,6 +832,28 @@ def test_config3_full_size_sampled_rows(hk):
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(2))[:96].sort().values.to(DEV)
     ref = gemm.gemm_mxfp4(ac[rows].cpu(), wc.cpu(), asc[rows].cpu(), wsc.cpu())
     _check(C[rows], ref, "config 3 full size, sampled rows")
+
+
+def test_config3_full_size_scale_byte_plus_one_doubles_every_output(hk):
+    """Config 3 at full size: raising every activation scale byte by one (x2 in e8m0) must double all 67 M bf16
+    outputs of the CTA-pair kernel bit for bit."""
+    M = N = K = 8192
+    g = torch.Generator(device=DEV).manual_seed(43)
+    A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
+    W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+    ac = torch.empty(M, K // 2, dtype=torch.uint8, device=DEV); asc = torch.empty(M, K // 32, dtype=torch.uint8, device=DEV)
+    wc = torch.empty(N, K // 2, dtype=torch.uint8, device=DEV); wsc = torch.empty(N, K // 32, dtype=torch.uint8, device=DEV)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(A, None, ac, asc, 1e-6)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, wc, wsc, 1e-6)
+    C1 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    C2 = torch.empty_like(C1)
+    hk.gemm.afp4wfp4.dispatch(ac, wc, C1, asc, wsc)
+    assert hk.last_kernel() == "gemm_mxfp4_pair_kernel<256x192>"
+    hk.gemm.afp4wfp4.dispatch(ac, wc, C2, asc + 1, wsc)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert int(asc.max()) < 254
+    assert torch.equal(C2, C1 * 2.0)
 
 
 def test_batched_gemm_mxfp4_wide_and_pair_kernels(hk):
