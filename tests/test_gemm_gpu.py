@@ -414,6 +414,38 @@ def test_moe_gemm_blockscale(hk, tokens, E, top_k, K, N, with_bias):
     _check(Y, ref, f"moe blockscale tokens={tokens} E={E}")
 
 
+def test_moe_gemm_blockscale_bench_size_equals_the_dense_kernel_expert_by_expert(hk):
+    """The grouped GEMM at the bench's size (8192 tokens x top-2 of 8 experts, N = 14336, K = 4096): every output row
+    must equal, bit for bit, what the dense block-scale GEMM gives for that expert's rows and weights (same tile
+    width, same K order) -- all 235 M outputs, ragged expert row counts included."""
+    tokens, E, top_k, K, N = 8192, 8, 2, 4096, 14336
+    g = torch.Generator(device=DEV).manual_seed(91)
+    X = torch.randn(tokens, K, generator=g, device=DEV).bfloat16()
+    xq = torch.empty(tokens, K, dtype=torch.uint8, device=DEV); xs = torch.empty(tokens, K // 128, device=DEV)
+    hk.fused_rmsnorm_fp8_quant_fwd(X, None, xq, xs, 1e-6)
+    wq = torch.empty(E, N, K, dtype=torch.uint8, device=DEV); ws = torch.empty(E, K // 128, N // 128, device=DEV)
+    for e in range(E):
+        W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+        hk.weight_quant_128x128(W, wq[e], ws[e])
+    hist, offs, gather, data = _routing(tokens, E, top_k, seed=9)
+    assert (hist % 128 != 0).any()
+    rows = tokens * top_k
+    Y = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gd = _dev(gather)
+    _moe_call(hk, xq, wq, Y, xs, ws, None, gd, _dev(hist), _dev(offs), _dev(data), top_k)
+    assert hk.last_kernel() == "gemm_fp8_kernel<256,blockscale,grouped>"
+    torch.cuda.synchronize()
+    _status_ok()
+    for e in range(E):
+        r0, r1 = int(offs[e]), int(offs[e] + hist[e])
+        tok = (gd[r0:r1] // top_k).long()
+        Ce = torch.empty(r1 - r0, N, dtype=torch.bfloat16, device=DEV)
+        hk.gemm.a8w8_blockscale.dispatch(xq[tok].contiguous(), wq[e], Ce, xs[tok].contiguous(), ws[e])
+        assert hk.last_kernel() == "gemm_fp8_kernel<256,blockscale>"
+        assert torch.equal(Y[r0:r1], Ce), f"expert {e}: grouped and dense results differ"
+    _status_ok()
+
+
 def test_moe_gemm_blockscale_reference_golden(hk, golden_dir):
     """The reference's own routing generator and reference function (group 128) on integer operands e4m3 holds exactly."""
     g = np.load(os.path.join(golden_dir, "moe_gemm_blockscale.npz"))
@@ -495,6 +527,39 @@ def test_moe_gemm_mxfp4(hk, tokens, E, top_k, K, N, mul):
     ref = gemm.moe_gemm_mxfp4(ac, wc, asc, wsc, a_scale, b_scale, ids, eids, w, total, top_k, mul_weight=mul, index="token")
     assert not torch.isnan(C.float()).any()               # every (token, k) row is named by the list
     _check(C, ref, f"moe mxfp4 tokens={tokens} E={E}")
+
+
+def test_moe_gemm_mxfp4_bench_size_equals_the_dense_kernel_expert_by_expert(hk):
+    """The grouped MXFP4 GEMM at the bench's size (8192 tokens x top-2 of 8 experts, N = K = 8192) with unit global
+    scales and no routing-weight multiply: every output row must equal, bit for bit, the dense MXFP4 GEMM of that
+    token's codes with its expert's weights (the dense call runs the CTA-pair kernel, the grouped one single CTAs:
+    the order of the K steps is the same)."""
+    tokens, E, top_k, K, N = 8192, 8, 2, 8192, 8192
+    g = torch.Generator(device=DEV).manual_seed(92)
+    X = torch.randn(tokens, K, generator=g, device=DEV).bfloat16()
+    ac = torch.empty(tokens, K // 2, dtype=torch.uint8, device=DEV); asc = torch.empty(tokens, K // 32, dtype=torch.uint8, device=DEV)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(X, None, ac, asc, 1e-6)
+    wc = torch.empty(E, N, K // 2, dtype=torch.uint8, device=DEV); wsc = torch.empty(E, N, K // 32, dtype=torch.uint8, device=DEV)
+    for e in range(E):
+        W = (torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16()
+        hk.fused_rmsnorm_mxfp4_quant_fwd(W, None, wc[e], wsc[e], 1e-6)
+    ids, eids, w, total = _moe_mxfp4_routing(tokens, E, top_k, seed=8)
+    C = torch.full((total, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    one = torch.ones(1, device=DEV)
+    _moe_mxfp4_call(hk, ac, wc, C, asc, wsc, one, torch.ones(E, device=DEV), _dev(w), _dev(ids), _dev(eids), total, top_k, False)
+    assert "grouped" in hk.last_kernel()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert not torch.isnan(C.float()).any()
+    blocks = ids.reshape(-1, 128)
+    for e in range(E):
+        flat = blocks[eids == e].ravel()
+        flat = torch.from_numpy(flat[flat < total]).long().to(DEV)
+        tok = flat // top_k
+        Ce = torch.empty(flat.numel(), N, dtype=torch.bfloat16, device=DEV)
+        hk.gemm.afp4wfp4.dispatch(ac[tok].contiguous(), wc[e], Ce, asc[tok].contiguous(), wsc[e])
+        assert torch.equal(C[flat], Ce), f"expert {e}: grouped and dense results differ"
+    _status_ok()
 
 
 def test_moe_gemm_mxfp4_reference_golden(hk, golden_dir):
