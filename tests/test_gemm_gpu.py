@@ -242,6 +242,67 @@ def test_gemm_per_token_large_variants(hk, shape, kernel):
     _sampled_rows_check(C, aq, bq, sa, sb, f"per-token {shape} {kernel}", nrows=256)
 
 
+def test_per_token_8192_cubed_every_element_vs_device_fp32_and_exact_properties(hk):
+    """The CTA-pair per-token kernel on 8192^3 (the shape its throughput is quoted on): all 67 M outputs against an
+    fp32 matmul of the dequantized operands on the device (torch, TF32 off: a checker); doubling a_scale doubles every
+    output exactly; permuting the rows of A permutes the rows of C exactly."""
+    M = N = K = 8192
+    g = torch.Generator(device=DEV).manual_seed(61)
+    aq = torch.empty(M, K, dtype=torch.uint8, device=DEV); sa = torch.empty(M, device=DEV)
+    bq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sb = torch.empty(N, device=DEV)
+    hk.per_token_quant_fwd(torch.randn(M, K, generator=g, device=DEV).bfloat16(), aq, sa)
+    hk.per_token_quant_fwd((torch.randn(N, K, generator=g, device=DEV) * 0.02).bfloat16(), bq, sb)
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    hk.gemm.a8w8_per_token.dispatch(aq, bq, C, sa, sb)
+    assert hk.last_kernel() == "gemm_fp8_kernel<256,pts,pair>"
+    C2 = torch.empty_like(C)
+    hk.gemm.a8w8_per_token.dispatch(aq, bq, C2, sa * 2.0, sb)
+    torch.cuda.synchronize()
+    assert torch.equal(C2, C * 2.0)
+    perm = torch.randperm(M, generator=torch.Generator().manual_seed(3)).to(DEV)
+    hk.gemm.a8w8_per_token.dispatch(aq[perm].contiguous(), bq, C2, sa[perm].contiguous(), sb)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.equal(C2, C[perm])
+    del C2
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = (aq.view(torch.float8_e4m3fn).float() * sa[:, None]) @ (bq.view(torch.float8_e4m3fn).float() * sb[:, None]).t()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+    err = float((C.float() - ref).abs().max() / ref.abs().max())
+    assert err <= TOL, err
+
+
+def test_ptgq_bench_size_every_element_vs_device_fp32(hk):
+    """The in-loop re-quantizing GEMM at the bench's size (4096 x 14336 x 4096): the activations quantized per row and
+    64-wide K group on the device with torch (amax / 448, e4m3 cast), dequantized, multiplied in fp32 (TF32 off) with the
+    decoded weights, scaled by b_scale, plus bias -- all 59 M outputs."""
+    M, N, K = 4096, 14336, 4096
+    g = torch.Generator(device=DEV).manual_seed(62)
+    A = torch.randn(1, M, K, generator=g, device=DEV).bfloat16()
+    wq = torch.empty(N, K, dtype=torch.uint8, device=DEV); sw = torch.empty(N, device=DEV)
+    hk.per_token_quant_fwd(torch.randn(N, K, generator=g, device=DEV).bfloat16(), wq, sw)      # any e4m3 codes will do
+    bias = torch.randn(1, 1, N, generator=g, device=DEV).bfloat16()
+    bs = torch.full((1,), 0.02, device=DEV)
+    C = torch.empty(1, M, N, dtype=torch.bfloat16, device=DEV)
+    hk.batched_gemm.a8w8_ptgq.dispatch(A, wq.view(1, N, K), bs, C, bias)
+    torch.cuda.synchronize()
+    _status_ok()
+    Ag = A[0].float().view(M, K // 64, 64)
+    a_scale = Ag.abs().amax(dim=2, keepdim=True).clamp_min(1e-10) * (1.0 / 448.0)
+    a_deq = ((Ag * (1.0 / a_scale)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * a_scale).view(M, K)
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = (a_deq @ wq.view(torch.float8_e4m3fn).float().t()) * 0.02 + bias[0].float()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+    err = float((C[0].float() - ref).abs().max() / ref.abs().max())
+    assert err <= TOL, err
+
+
 _SUBPROCESS_CASE = r"""
 import json, os, sys
 import numpy as np, torch
