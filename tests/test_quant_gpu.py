@@ -197,3 +197,41 @@ def test_round_trip_property_at_full_size(hk):
     assert ((dq - xf).abs() <= xf.abs() * 0.0626 + s * 2 ** -10).all()
     assert ((q & 0x7F).amax(dim=1) == 0x7E).all()
     assert torch.equal(s.flatten(), (xf.abs().amax(1) / torch.tensor(448.0, device=DEV)).clamp(min=1e-10))
+
+
+def test_block_quantizers_bit_exact_at_the_bandwidth_benchmark_size(hk):
+    """1x128 FP8 and MXFP4 (default mode) on 16384 x 8192 -- the size their GB/s is quoted on -- against the same
+    rules evaluated with torch on the device (a checker; IEEE fp32 division and torch's e4m3fn cast, which the CPU
+    tier pins against the oracle's): every code and every scale of all 134 M elements."""
+    M, D = 16384, 8192
+    x = torch.randn(M, D, device=DEV, dtype=torch.bfloat16)
+    x[:, 7] *= 37.0
+    x[5] = 0.0                                                  # an all-zero row: floor scale, zero codes / byte 0
+    xf = x.float()
+    # 1 x 128 FP8
+    q = torch.empty(M, D, dtype=torch.uint8, device=DEV); s = torch.empty(M, D // 128, device=DEV)
+    hk.fused_rmsnorm_fp8_quant_fwd(x, None, q, s, 1e-6)
+    g = xf.view(M, D // 128, 128)
+    scale = (g.abs().amax(dim=2, keepdim=True) / torch.tensor(448.0, device=DEV)).clamp_min(oracle_floor())    # tensor / tensor: a true division
+    ref = (g / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).view(M, D)
+    assert torch.equal(s, scale.view(M, D // 128))
+    assert torch.equal(q, ref)
+    del q, s, ref, scale, g
+    # MXFP4, mode "doc": e = floor(log2 amax) - 2, nearest E2M1 magnitude with ties to the smaller one
+    c = torch.empty(M, D // 2, dtype=torch.uint8, device=DEV); sb = torch.empty(M, D // 32, dtype=torch.uint8, device=DEV)
+    hk.fused_rmsnorm_mxfp4_quant_fwd(x, None, c, sb, 1e-6)
+    g = xf.view(M, D // 32, 32)
+    amax = g.abs().amax(dim=2)
+    e = torch.where(amax > 0, torch.frexp(amax)[1] - 1 - 2, torch.full_like(amax, -127, dtype=torch.int32)).clamp(-127, 127)
+    assert torch.equal(sb, (e + 127).to(torch.uint8))
+    a = (g * torch.ldexp(torch.ones_like(amax), -e)[..., None]).abs()          # exact: power-of-two scaling
+    mag = torch.zeros_like(a, dtype=torch.uint8)
+    for mid in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0):
+        mag += (a > mid).to(torch.uint8)
+    nib = (mag | ((g < 0).to(torch.uint8) << 3)).view(M, D)
+    assert torch.equal(c, nib[:, 0::2] | (nib[:, 1::2] << 4))
+
+
+def oracle_floor():
+    from oracle import quant
+    return float(quant.SCALE_FLOOR)
