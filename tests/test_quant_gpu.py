@@ -232,6 +232,22 @@ def test_block_quantizers_bit_exact_at_the_bandwidth_benchmark_size(hk):
     assert torch.equal(c, nib[:, 0::2] | (nib[:, 1::2] << 4))
 
 
+def test_weight_quantizer_bit_exact_at_config5_size(hk):
+    """128 x 128 block FP8 weight quantizer on config 5's weight (57344 x 8192): every code and scale against the rule
+    evaluated with torch on the device (true division, torch's e4m3fn cast)."""
+    N, K = 57344, 8192
+    w = (torch.randn(N, K, device=DEV) * 0.02).bfloat16()
+    w[130:200, 4096:4100] = 0.0
+    q = torch.empty(N, K, dtype=torch.uint8, device=DEV); s = torch.empty(K // 128, N // 128, device=DEV)
+    hk.weight_quant_128x128(w, q, s)
+    t = w.float().view(N // 128, 128, K // 128, 128)
+    scale = (t.abs().amax(dim=(1, 3), keepdim=True) / torch.tensor(448.0, device=DEV)).clamp_min(oracle_floor())
+    assert torch.equal(s, scale.view(N // 128, K // 128).t())
+    for n0 in range(0, N // 128, 64):                    # the fp32 temporaries of 64 row blocks at a time
+        ref = (t[n0:n0 + 64] / scale[n0:n0 + 64]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        assert torch.equal(q[n0 * 128:(n0 + 64) * 128], ref.view(-1, K))
+
+
 def oracle_floor():
     from oracle import quant
     return float(quant.SCALE_FLOOR)
