@@ -127,3 +127,24 @@ def test_shapes_are_validated(hk):
         q.downcast_to_mxfp(torch.zeros(4, 48, dtype=torch.uint8, device=DEV), torch.zeros(4, 1, dtype=torch.uint8, device=DEV), x, 4, 48, False)
     with pytest.raises(RuntimeError, match="outer_dim\\*quant_dim"):
         q.downcast_to_mxfp(torch.zeros(4, 64, dtype=torch.uint8, device=DEV), torch.zeros(4, 2, dtype=torch.uint8, device=DEV), x, 4, 64, False)
+
+
+@pytest.mark.parametrize("is_fp4", [False, True])
+def test_casts_at_the_bandwidth_benchmark_size_sampled_rows_bit_exact(hk, is_fp4):
+    """16384 x 8192, the size the casts' GB/s is quoted on: 128 sampled rows of the down-cast (codes and scale bytes)
+    and of the up-cast of the whole result against the oracle, bit for bit."""
+    M, D = 16384, 8192
+    g = torch.Generator(device=DEV).manual_seed(17)
+    src = torch.randn(M, D, generator=g, device=DEV).bfloat16()
+    src[:, 5] *= 100.0
+    src[3] = 0.0
+    q = hk.moe_routing.quant
+    t = torch.empty(M, D // (2 if is_fp4 else 1), dtype=torch.uint8, device=DEV); s = torch.empty(M, D // 32, dtype=torch.uint8, device=DEV)
+    q.downcast_to_mxfp(t, s, src, M, D, is_fp4)
+    out = torch.empty(M, D, dtype=torch.bfloat16, device=DEV)
+    q.upcast_from_mxfp(out, s, t, M, D, is_fp4)
+    torch.cuda.synchronize()
+    rows = torch.cat([torch.tensor([0, 3, M - 1]), torch.randperm(M, generator=torch.Generator().manual_seed(4))[:125]]).to(DEV)
+    rc, rs = qm.downcast_to_mxfp(src[rows].cpu(), is_fp4)
+    assert np.array_equal(t[rows].cpu().numpy(), rc) and np.array_equal(s[rows].cpu().numpy(), rs)
+    assert np.array_equal(_bits(out[rows]), qm.upcast_from_mxfp(rc, rs, is_fp4))
