@@ -960,9 +960,9 @@ def test_config3_full_size_sampled_rows(hk):
     _check(C[rows], ref, "config 3 full size, sampled rows")
 
 
-def test_config3_full_size_scale_byte_plus_one_doubles_every_output(hk):
+def test_config3_full_size_every_element_and_exact_scale_doubling(hk):
     """Config 3 at full size: raising every activation scale byte by one (x2 in e8m0) must double all 67 M bf16
-    outputs of the CTA-pair kernel bit for bit."""
+    outputs of the CTA-pair kernel bit for bit; and all of them against an fp32 matmul on the device."""
     M = N = K = 8192
     g = torch.Generator(device=DEV).manual_seed(43)
     A = torch.randn(M, K, generator=g, device=DEV).bfloat16()
@@ -980,6 +980,22 @@ def test_config3_full_size_scale_byte_plus_one_doubles_every_output(hk):
     _status_ok()
     assert int(asc.max()) < 254
     assert torch.equal(C2, C1 * 2.0)
+    del C2
+    # every element against an fp32 matmul of the decoded operands on the device (torch, TF32 off: a checker)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device=DEV)
+
+    def decode(codes, sbytes):
+        v = torch.stack([lut[(codes & 0xF).long()], lut[(codes >> 4).long()]], dim=-1).view(codes.shape[0], -1)
+        return v * torch.ldexp(torch.ones_like(sbytes, dtype=torch.float32), sbytes.int() - 127).repeat_interleave(32, dim=1)
+
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = decode(ac, asc) @ decode(wc, wsc).t()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+    err = float((C1.float() - ref).abs().max() / ref.abs().max())
+    assert err <= TOL, err
 
 
 def test_batched_gemm_mxfp4_wide_and_pair_kernels(hk):
