@@ -605,6 +605,28 @@ def tensor_peak_probe(kind, target_ms=80.0):
     return flop.value / 1e12 / (ms / 1e3), ms
 
 
+_JSON_FD = None
+
+
+def keep_stdout_for_the_json_line():
+    """Everything a library prints on stdout from here on (NCCL's version banner at the first collective) goes to
+    stderr; the one JSON line is written to the original stdout by `emit`."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    line = (json.dumps(obj) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        os.write(1, line)
+    else:
+        os.write(_JSON_FD, line)
+
+
 def run_peak(args, name, dev):
     """`--workload peak-fp8|peak-fp4`: the ceiling probe as a bench line of its own."""
     kind = 0 if name == "peak-fp8" else 1
@@ -630,7 +652,7 @@ def run_peak(args, name, dev):
                         "peak_source": f"{mult:g} x dense bf16 cuBLAS sustained ({peaks['source']})",
                         "frac_of_spec": tf / (4500.0 if kind == 0 else 9000.0)},
            "cpu_baseline": None, "e2e": None, "gpu_launches": len(vals), "clocks": clocks}
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 def run_timeline(args, dev):
@@ -673,7 +695,7 @@ def run_timeline(args, dev):
            "stage_back_to_operands_seen": med((full[:, 11:59] - prod[:, 11:59])),
            "warp_lateness_by_quarter": [round(float(np.median(late[:, [q, q + 4]])), 1) for q in range(4)],
            "note": "warps of quarter q run on scheduler q; the MMA-issuing warp is on scheduler 1, the TMA producer on scheduler 0"}
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 def shard_check(wl, nrows=64):
@@ -816,7 +838,7 @@ def run_reference(args, name, world):
            "cpu_baseline": {"value": value, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
                             "note": "CPU oracle (torch CPU fp32 dequantize-then-matmul + NumPy quantizers), bounded sample"},
            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 def main():
@@ -835,6 +857,7 @@ def main():
         args.no_cpu_baseline = args.no_e2e = True
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    keep_stdout_for_the_json_line()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -846,7 +869,7 @@ def main():
         return 0
 
     if not torch.cuda.is_available():
-        print(json.dumps({"error": "no CUDA device; this path has no CPU fallback"}))
+        emit({"error": "no CUDA device; this path has no CPU fallback"})
         return 1
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -1082,7 +1105,7 @@ def main():
             e2e["host_cores"] = (f"{len(near_cores)} cores nearest the GPU (NVML affinity), pinned buffers allocated from there"
                                  if near_cores else "process affinity unchanged")
         out.update(extras)
-        print(json.dumps(out), flush=True)
+        emit(out)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
