@@ -206,3 +206,34 @@ def test_mxfp4_gemm_refuses_the_host_dequantized_three_argument_form(hk):
     x = torch.zeros(128, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="packed e2m1"):
         hk.gemm.afp4wfp4.dispatch(x, x, x)
+
+
+def test_header_is_plain_c_and_a_c_program_links_against_the_library(tmp_path):
+    """include/hkb200.h must compile as strict C99 (no C++ in the boundary) and a C caller must link and get error
+    codes, not crashes, without a GPU: the form in which a cgo / JNI / ctypes binding sees the library."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "amd-kernels_b200", "kernels")
+    src = tmp_path / "caller.c"
+    src.write_text(r'''
+#include "hkb200.h"
+#include <stdio.h>
+int main(void) {
+    int64_t n0 = 0, n1 = 0;
+    int rc = hkb_shard_bounds(57344, 8, 3, &n0, &n1);
+    printf("%d %d %lld %lld\n", hkb_version(), rc, (long long)n0, (long long)n1);
+    rc = hkb_gemm_fp8_blockscale(0, 0, 0, 0, 0, 128, 128, 128, 128, 0);
+    printf("%d %s\n", rc, hkb_last_error());
+    return 0;
+}
+''')
+    exe = tmp_path / "caller"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(root, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-lhkb200", "-Wl,-rpath," + libdir], check=True, capture_output=True, text=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines()
+    assert out[0].split() == ["200", "0", "21504", "28672"]
+    assert out[1].startswith("-1 ") and "null pointer" in out[1]
