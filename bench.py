@@ -24,10 +24,12 @@ synthetic tensors, there is no dataset behind this metric):
   ptgq bf16 activations quantized per row and 64-wide K group inside the GEMM, scalar weight scale, on config 2's shape
   qbw-fp8 / qbw-1x128 / qbw-mxfp4 / qbw-mxfp4-16k   quantizer bandwidth runs (16384x8192, 16384x8192, 8192x8192, 16384x8192)
   peak-fp8 / peak-fp4   tensor-core ceiling probe: back-to-back tcgen05.mma on resident operands, all SMs
+  timeline  c5s through the diagnostic build of the block-scale kernel: where the clocks of a K block go (its own JSON line)
 
 At --gpus N > 1 the line also carries `shard_check` (sampled rows of every rank's shard against an
 fp32 product on the device, untimed), `gemm_plus_gather` (the sharded GEMM followed by the opt-in
-NCCL all-gather of the bf16 shards, timed beside the GEMM alone) and an `e2e` in which every rank
+NCCL all-gather of the bf16 shards, timed beside the GEMM alone), `gemm_fused_gather` (the same result with the
+gather fused into the GEMM's epilogue: stores to every rank's matrix over NVLink) and an `e2e` in which every rank
 uploads only its M/N rows of the activations, quantizes them and all-gathers codes and scales over
 NVLink (the replicated-upload form is reported beside it).
 
